@@ -1,0 +1,14 @@
+"""B200-native implementation of the FlagAttention operators.
+
+Drop-in for the `flag_attn` package: `import flagattention_b200 as flag_attn`.
+Everything computes in hand-written sm_100a CUDA kernels behind the C ABI of
+libflagattn_b200.so; importing the package does not need a GPU, calling an
+operator does.
+"""
+__version__ = "0.1.0"
+
+from .piecewise import attention as piecewise_attention  # noqa: F401
+from .flash import attention as flash_attention  # noqa: F401
+from .split_kv import attention as flash_attention_split_kv  # noqa: F401
+from .paged import attention as paged_attention  # noqa: F401
+from . import testing  # noqa: F401

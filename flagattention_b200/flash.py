@@ -1,0 +1,156 @@
+"""flash_attention: host side of the B200 kernels.
+
+Mirrors the operator interface of the reference (src/flag_attn/flash.py:23-286):
+same argument names, same return structure (the output alone, or the 5-tuple
+when any return_* flag is set), same AssertionErrors on bad shapes, autograd
+through q, k, v only.  The kernels run on the current CUDA stream of the
+inputs' device.
+"""
+import math
+
+import torch
+
+from . import _C
+from .split_kv import get_fwd_config as get_fwd_config_kv_split
+from .split_kv import num_splits_herustic, _splitkv_forward
+
+__all__ = ["attention"]
+
+
+def get_fwd_config(B, H, M, N, D, causal):
+    """Tile shape used by the one-pass forward kernel: (BLOCK_M, BLOCK_N, stages, warps).
+    Kept for interface compatibility (src/flag_attn/flash.py:290-322); the tile
+    shape is compiled into the kernels, so overriding this has no effect."""
+    return (128, 64, 2, 8)
+
+
+def get_bwd_config(B, H, M, N, D, causal):
+    """Counterpart of src/flag_attn/flash.py:493-519; informational only."""
+    return (64, 128, 2, 8)
+
+
+def _forward(q, k, v, causal, sm_scale):
+    B, H, M, D = q.shape
+    N, Hk = k.shape[2], k.shape[1]
+    lib = _C.load()
+    o = torch.empty_like(q) if q.is_contiguous() else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    L = torch.empty((B, H, M), device=q.device, dtype=torch.float32)
+    shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
+    tq, tk, tv, to = _C.tensor4(q), _C.tensor4(k), _C.tensor4(v), _C.tensor4(o)
+    st = lib.fa_flash_fwd(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv), _C.byref(to),
+                          _C.fptr(L), _C.stream_ptr(q.device))
+    _C.check(st, "fa_flash_fwd")
+    return o, L
+
+
+def _total_attention(q, k, L, causal, sm_scale):
+    B, H, M, D = q.shape
+    N, Hk = k.shape[2], k.shape[1]
+    lib = _C.load()
+    tot = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+    shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
+    tq, tk = _C.tensor4(q), _C.tensor4(k)
+    st = lib.fa_total_attention(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.fptr(L),
+                                _C.fptr(tot), _C.stream_ptr(q.device))
+    _C.check(st, "fa_total_attention")
+    return tot
+
+
+class FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, dropout_p, return_log_normalizer,
+                return_total_attention, return_seed_offset):
+        Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+        assert Dq == Dk == Dv, "feature size of q, k, v should be equal"
+        assert Dk in {16, 32, 64, 128}
+        assert dropout_p == 0.0, "dropout is not implemented by the B200 kernels"
+        assert q.is_cuda and k.is_cuda and v.is_cuda, "inputs must be CUDA tensors"
+        assert q.dtype == k.dtype == v.dtype
+
+        B, H, M, D = q.shape
+        N = k.shape[2]
+        Hk, Hv = k.shape[1], v.shape[1]
+        assert Hk == Hv, "num of heads in k and v should be equal"
+        assert H % Hk == 0, "number of heads in q must be a multiple of that in k & v"
+
+        if sm_scale is None:
+            sm_scale = 1. / math.sqrt(D)
+
+        q, k, v = _C.kernel_ready(q), _C.kernel_ready(k), _C.kernel_ready(v)
+
+        with torch.cuda.device(q.device):
+            num_sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+            cfg = get_fwd_config_kv_split(B, H, M, N, D, causal)
+            S = num_splits_herustic(B, H, M, N, cfg[0], cfg[1], num_sms, 128)
+            if S > 1:
+                o, L = _splitkv_forward(q, k, v, causal, sm_scale, S)
+            else:
+                o, L = _forward(q, k, v, causal, sm_scale)
+            tot_attn = None
+            if return_total_attention:
+                tot_attn = _total_attention(q, k, L, causal, sm_scale)
+
+        ctx.save_for_backward(q, k, v, o, L)
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+
+        has_extra_return = True in (return_log_normalizer, return_total_attention, return_seed_offset)
+        if has_extra_return:
+            # seed / offset are only produced with dropout, which is not built
+            return (o, L if return_log_normalizer else None, tot_attn, None, None)
+        return o
+
+    @staticmethod
+    def backward(ctx, do, *ignored):
+        q, k, v, o, L = ctx.saved_tensors
+        sm_scale, causal = ctx.sm_scale, ctx.causal
+        B, H, M, D = q.shape
+        N, Hk = k.shape[2], k.shape[1]
+        lib = _C.load()
+        do = _C.kernel_ready(do)
+
+        with torch.cuda.device(q.device):
+            stream = _C.stream_ptr(q.device)
+            shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
+            delta = torch.empty_like(L)
+            tq, tk, tv, to, tdo = (_C.tensor4(x) for x in (q, k, v, o, do))
+            st = lib.fa_flash_bwd_delta(_C.byref(shape), _C.byref(to), _C.byref(tdo),
+                                        _C.fptr(delta), stream)
+            _C.check(st, "fa_flash_bwd_delta")
+
+            # dk / dv come out with Hk heads: the group sum is done in the kernel
+            dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=q.device)
+            dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=q.device)
+            tdk, tdv = _C.tensor4(dk), _C.tensor4(dv)
+            st = lib.fa_flash_bwd_dkdv(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
+                                       _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdk),
+                                       _C.byref(tdv), stream)
+            _C.check(st, "fa_flash_bwd_dkdv")
+
+            dq = torch.empty((B, H, M, D), dtype=q.dtype, device=q.device)
+            tdq = _C.tensor4(dq)
+            st = lib.fa_flash_bwd_dq(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
+                                     _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdq),
+                                     stream)
+            _C.check(st, "fa_flash_bwd_dq")
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def attention(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
+              return_log_normalizer=False, return_total_attention=False, return_seed_offset=False):
+    """FlashAttention forward/backward on B200.
+
+    Arguments:
+        q: (batch, heads_q, seqlen_q, headdim); k, v: (batch, heads_k, seqlen_k, headdim),
+           fp16 or bf16 CUDA tensors, heads_q a multiple of heads_k, headdim in {16,32,64,128}.
+        causal: bottom-right aligned causal mask.
+        sm_scale: softmax scale, default 1/sqrt(headdim).
+        dropout_p: must be 0.0 (dropout is not built).
+        return_log_normalizer / return_total_attention / return_seed_offset: when any is
+           set, returns (out, log_normalizer | None, total_attention | None, None, None).
+
+    Returns out, shape of q; log_normalizer (batch, heads_q, seqlen_q) fp32;
+    total_attention (batch, heads_q, seqlen_k) fp32.
+    """
+    return FlashAttention.apply(q, k, v, causal, sm_scale, dropout_p, return_log_normalizer,
+                                return_total_attention, return_seed_offset)

@@ -1,0 +1,75 @@
+"""Plain-PyTorch reference implementations shipped with the package, the
+counterpart of `flag_attn.testing` (src/flag_attn/testing/__init__.py:1-4).
+
+They run on any device torch supports and exist so that users can check the
+kernels the way the reference's README describes: compare against
+`upcast=True` (fp32 math) and require the kernel's error to be at most twice
+that of the same-precision PyTorch path.  They materialise the full score
+matrix, so memory grows with seqlen_q * seqlen_k.
+"""
+import math
+
+import torch
+
+__all__ = ["flash_attention", "piecewise_attention", "paged_attention"]
+
+
+def _causal_mask(m, n, device):
+    return (torch.arange(m, device=device)[:, None] + (n - m)) >= torch.arange(n, device=device)
+
+
+def flash_attention(q, k, v, causal, dropout_p=0.0, dropout_mask=None, sm_scale=None,
+                    return_log_normalizer=False, return_total_attention=False, upcast=False):
+    assert dropout_p == 0.0 and dropout_mask is None, "dropout is not built"
+    dtype = q.dtype
+    if upcast:
+        q, k, v = q.float(), k.float(), v.float()
+    scale = sm_scale if sm_scale is not None else q.shape[-1] ** -0.5
+    groups = q.shape[1] // k.shape[1]
+    if groups > 1:
+        k, v = k.repeat_interleave(groups, 1), v.repeat_interleave(groups, 1)
+    s = torch.matmul(q, k.transpose(2, 3)) * scale
+    keep = _causal_mask(q.shape[2], k.shape[2], q.device) if causal else None
+    if causal:
+        s = s.masked_fill(~keep, float("-inf"))
+    s = s.float()
+    p = torch.softmax(s, dim=-1, dtype=torch.float32)
+    if causal:
+        p = p.masked_fill(~keep, 0.0)
+    o = torch.matmul(p.to(v.dtype), v).to(dtype)
+    if return_log_normalizer or return_total_attention:
+        return (o, torch.logsumexp(s, dim=-1) if return_log_normalizer else None,
+                p.sum(dim=-2) if return_total_attention else None)
+    return o
+
+
+def piecewise_attention(q1, k1, q2, k2, v, dist_threshold, causal, sm_scale=None, upcast=False):
+    dtype = q1.dtype
+    if upcast:
+        q1, k1, q2, k2, v = q1.float(), k1.float(), q2.float(), k2.float(), v.float()
+    scale = sm_scale if sm_scale is not None else q1.shape[-1] ** -0.5
+    m, n = q1.shape[2], k1.shape[2]
+    dist = (torch.arange(m, device=q1.device)[:, None] + (n - m)) - torch.arange(n, device=q1.device)
+    s = torch.where(dist >= dist_threshold, torch.matmul(q2, k2.transpose(2, 3)),
+                    torch.matmul(q1, k1.transpose(2, 3))) * scale
+    if causal:
+        s = s.masked_fill(dist < 0, torch.finfo(s.dtype).min)
+    p = torch.softmax(s, dim=-1, dtype=torch.float32).to(v.dtype)
+    if causal:
+        p = p.masked_fill(dist < 0, 0.0)
+    return torch.matmul(p, v).to(dtype)
+
+
+def paged_attention(query, key_cache, value_cache, block_tables, context_lens, scale):
+    """Note the argument order: block_tables comes before context_lens here."""
+    out = torch.empty_like(query)
+    kv_heads, block, head = value_cache.shape[1:]
+    groups = query.shape[1] // kv_heads
+    for i, ctx in enumerate(context_lens.tolist()):
+        ids = block_tables[i, : (ctx + block - 1) // block].long()
+        kk = key_cache[ids].transpose(0, 1).reshape(kv_heads, -1, head)[:, :ctx].float()
+        vv = value_cache[ids].transpose(0, 1).reshape(kv_heads, -1, head)[:, :ctx].float()
+        qq = query[i].float().view(kv_heads, groups, head)
+        p = torch.softmax(torch.bmm(qq, kk.transpose(1, 2)) * scale, dim=-1)
+        out[i] = torch.bmm(p, vv).reshape(-1, head).to(out.dtype)
+    return out

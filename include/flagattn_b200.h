@@ -1,0 +1,208 @@
+/*
+ * flagattn_b200.h -- C ABI of libflagattn_b200.so
+ *
+ * Hand-written sm_100a CUDA implementations of the three FlagAttention
+ * operators (flash_attention fwd+bwd, piecewise_attention fwd+bwd,
+ * paged_attention decode).  Every entry point
+ *   - takes raw device pointers, sizes and ELEMENT strides (no torch types),
+ *   - enqueues its kernels on the CUDA stream passed as `stream` (a
+ *     cudaStream_t cast to void*; NULL = the legacy default stream) on the
+ *     device that is current on the calling thread,
+ *   - never allocates, never synchronises, never throws,
+ *   - returns FA_OK (0) or a negative fa_status.
+ * The caller owns all memory.  Inner-most (head_dim) stride is always 1 and
+ * every row start must be 16-byte aligned (pointer % 16 == 0, all other
+ * strides % 8 == 0 elements); the Python host makes a contiguous copy when a
+ * tensor does not satisfy this, exactly where the reference copies when
+ * stride(-1) != 1 (src/flag_attn/flash.py:14-17,44).
+ *
+ * Each declaration cites the reference interface it replaces, by path inside
+ * the FlagOpen/FlagAttention project.
+ */
+#ifndef FLAGATTN_B200_H_
+#define FLAGATTN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fa_status {
+  FA_OK = 0,
+  FA_ERR_BAD_ARG = -1,       /* NULL pointer, negative size, bad enum      */
+  FA_ERR_UNSUPPORTED = -2,   /* head_dim / dtype / group size not built    */
+  FA_ERR_ALIGNMENT = -3,     /* pointer or stride breaks the 16-byte rule  */
+  FA_ERR_LAUNCH = -4,        /* cudaGetLastError() != cudaSuccess          */
+  FA_ERR_WORKSPACE = -5,     /* workspace pointer missing or too small     */
+  FA_ERR_TOO_LARGE = -6      /* request exceeds a fixed built-in capacity  */
+} fa_status;
+
+typedef enum fa_dtype { FA_F16 = 0, FA_BF16 = 1 } fa_dtype;
+
+/* A (B, H, L, D) operand with arbitrary b/h/l element strides, d-stride 1. */
+typedef struct fa_tensor4 {
+  void *ptr;
+  int64_t stride_b, stride_h, stride_l;
+} fa_tensor4;
+
+/* ---------------------------------------------------------------------- */
+/* flash_attention                                                         */
+/* ---------------------------------------------------------------------- */
+
+/* Problem description shared by all flash entry points.
+ * q:(B,H,M,D)  k,v:(B,Hk,N,D), H % Hk == 0, D in {16,32,64,128}.
+ * Causal masking is bottom-right aligned: key n is visible to query m iff
+ * m + (N - M) >= n  (src/flag_attn/flash.py:37,442). */
+typedef struct fa_flash_shape {
+  int32_t dtype;     /* fa_dtype of q,k,v,o,do,dq,dk,dv */
+  int32_t B, H, Hk, M, N, D;
+  int32_t causal;
+  float sm_scale;
+} fa_flash_shape;
+
+/* Forward: o = softmax(sm_scale * q k^T [+causal]) v, lse = natural-log
+ * logsumexp of the scaled masked scores, fp32 (B,H,M) contiguous; rows with
+ * no visible key give o = 0, lse = -inf.
+ * Replaces the launch of `_fwd_kernel` in FlashAttention.forward
+ * (src/flag_attn/flash.py:64-87; kernel :325-489). */
+int fa_flash_fwd(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                 const fa_tensor4 *v, const fa_tensor4 *o, float *lse, void *stream);
+
+/* Split-KV forward for small M.  Stage 1 writes, per split, a normalised
+ * fp32 partial output (B,H,S,M,D) and its fp32 log-normaliser (B,H,S,M);
+ * stage 2 combines them into o and lse.  `n_split_size` keys per split, a
+ * multiple of 64.
+ * Replaces `_fwd_split_kv_kernel` + `_fwd_combine_kv_splits`
+ * (src/flag_attn/split_kv.py:14-227; launches src/flag_attn/flash.py:88-125,
+ * src/flag_attn/split_kv.py:295-328). */
+int fa_splitkv_fwd(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                   const fa_tensor4 *v, int32_t num_splits, int32_t n_split_size,
+                   float *o_partial, float *lse_partial, void *stream);
+int fa_splitkv_combine(const fa_flash_shape *s, int32_t num_splits, const float *o_partial,
+                       const float *lse_partial, const fa_tensor4 *o, float *lse, void *stream);
+/* Bytes of o_partial + lse_partial for a given problem (host-only helper). */
+int64_t fa_splitkv_workspace_bytes(const fa_flash_shape *s, int32_t num_splits);
+
+/* The split-count heuristic of the reference, restated
+ * (src/flag_attn/split_kv.py:234-262); host-only, no CUDA call. */
+int32_t fa_num_splits_heuristic(int32_t B, int32_t H, int32_t M, int32_t N, int32_t block_m,
+                                int32_t block_n, int32_t num_sms, int32_t max_splits);
+
+/* total[b,h,n] = sum_m P[m,n] recomputed from lse, fp32 (B,H,N) contiguous.
+ * Replaces `_total_attention_kernel` (src/flag_attn/total.py:50-142; launch
+ * src/flag_attn/flash.py:128-140). */
+int fa_total_attention(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                       const float *lse, float *total, void *stream);
+
+/* delta[b,h,m] = sum_d o*do, fp32 (B,H,M) contiguous.
+ * Replaces `_bwd_preprocess` (src/flag_attn/flash.py:522-568, launch :191-202;
+ * src/flag_attn/piecewise.py:407-447). */
+int fa_flash_bwd_delta(const fa_flash_shape *s, const fa_tensor4 *o, const fa_tensor4 *d_o,
+                       float *delta, void *stream);
+
+/* dk, dv with Hk heads: the sum over the query heads of a GQA group is taken
+ * inside the kernel.  Replaces `_bwd_kv_kernel` and the host-side group sum
+ * (src/flag_attn/flash.py:204-227,250-251; kernel :571-745). */
+int fa_flash_bwd_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                      const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                      const float *delta, const fa_tensor4 *dk, const fa_tensor4 *dv,
+                      void *stream);
+
+/* dq, fully overwritten, no atomics.  Replaces `_bwd_q_kernel`
+ * (src/flag_attn/flash.py:229-249; kernel :748-909). */
+int fa_flash_bwd_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                    const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                    const float *delta, const fa_tensor4 *dq, void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* piecewise_attention                                                     */
+/* ---------------------------------------------------------------------- */
+
+/* Score of (m, n) is q2.k2 when (m + N - M) - n >= dist_threshold, else q1.k1
+ * (src/flag_attn/piecewise.py:311,328-330).  No GQA: `s->Hk` must equal
+ * `s->H`.  Same lse / empty-row conventions as fa_flash_fwd.
+ * Replaces `_fwd_kernel` of piecewise (src/flag_attn/piecewise.py:54-69,
+ * kernel :223-370). */
+int fa_piecewise_fwd(const fa_flash_shape *s, int32_t dist_threshold, const fa_tensor4 *q1,
+                     const fa_tensor4 *k1, const fa_tensor4 *q2, const fa_tensor4 *k2,
+                     const fa_tensor4 *v, const fa_tensor4 *o, float *lse, void *stream);
+
+/* Replaces piecewise `_bwd_kv_kernel` (src/flag_attn/piecewise.py:114-139,
+ * kernel :450-627). */
+int fa_piecewise_bwd_dkdv(const fa_flash_shape *s, int32_t dist_threshold, const fa_tensor4 *q1,
+                          const fa_tensor4 *k1, const fa_tensor4 *q2, const fa_tensor4 *k2,
+                          const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                          const float *delta, const fa_tensor4 *dk1, const fa_tensor4 *dk2,
+                          const fa_tensor4 *dv, void *stream);
+
+/* Replaces piecewise `_bwd_q_kernel` (src/flag_attn/piecewise.py:141-164,
+ * kernel :630-792). */
+int fa_piecewise_bwd_dq(const fa_flash_shape *s, int32_t dist_threshold, const fa_tensor4 *q1,
+                        const fa_tensor4 *k1, const fa_tensor4 *q2, const fa_tensor4 *k2,
+                        const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                        const float *delta, const fa_tensor4 *dq1, const fa_tensor4 *dq2,
+                        void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* paged_attention (single-token decode over a block-table KV cache)       */
+/* ---------------------------------------------------------------------- */
+
+typedef struct fa_paged_args {
+  int32_t dtype;                 /* fa_dtype of query, caches and out              */
+  int32_t num_seqs, num_q_heads, num_kv_heads, head_size, block_size;
+  int32_t max_context_len;       /* host upper bound of context_lens               */
+  int32_t block_table_is_i64;    /* 0: int32 entries, 1: int64 entries             */
+  int32_t partition_size;        /* 0: one pass per (seq, kv head); else tokens    */
+                                 /* per split-KV partition, a multiple of 16       */
+  float attn_scale;
+  const void *query;             /* [num_seqs, num_q_heads, head_size]             */
+  int64_t q_stride_s, q_stride_h;
+  const void *key_cache;         /* [num_blocks, num_kv_heads, block_size, head]   */
+  const void *value_cache;       /* same strides as key_cache                      */
+  int64_t kv_stride_b, kv_stride_h, kv_stride_t;
+  const int32_t *context_lens;   /* [num_seqs]                                     */
+  const void *block_tables;      /* [num_seqs, max_blocks_per_seq]                 */
+  int64_t bt_stride_s;
+  void *out;                     /* [num_seqs, num_q_heads, head_size]             */
+  int64_t o_stride_s, o_stride_h;
+  /* split-KV workspace, used only when partition_size > 0; P = number of
+   * partitions = ceil(max_context_len / partition_size):                          */
+  float *part_out;               /* [num_seqs, num_q_heads, P, head_size] fp32     */
+  float *part_max;               /* [num_seqs, num_q_heads, P] fp32, base-2 domain */
+  float *part_sum;               /* [num_seqs, num_q_heads, P] fp32                */
+} fa_paged_args;
+
+/* Token j of sequence i is read at
+ * cache[block_tables[i, j / block_size], kv_head, j % block_size, :]; entries
+ * of block_tables past ceil(context_len / block_size) are never read.
+ * With partition_size == 0 writes `out`; otherwise writes the workspace for
+ * every partition that starts below context_len.
+ * Replaces `_paged_attn_kernel` (src/flag_attn/paged.py:56-88,112-143; kernel
+ * :194-349). */
+int fa_paged_decode(const fa_paged_args *a, void *stream);
+
+/* Combines the partitions written by fa_paged_decode into `out`.
+ * Replaces `_paged_attn_v2_reduce_kernel` (src/flag_attn/paged.py:145-162;
+ * kernel :352-435). */
+int fa_paged_reduce(const fa_paged_args *a, void *stream);
+
+/* Bytes needed for part_out + part_max + part_sum (host-only helper). */
+int64_t fa_paged_workspace_bytes(const fa_paged_args *a);
+
+/* Test hook for "integer block-table indexing is bit-exact": writes, for
+ * every (seq, logical block < ceil(context_len / block_size)), the physical
+ * block id the decode kernel would gather from into visited[seq, block]
+ * (int64, row stride = max_blocks), and -1 elsewhere. */
+int fa_paged_trace_blocks(const fa_paged_args *a, int64_t *visited, int32_t max_blocks,
+                          void *stream);
+
+/* ---------------------------------------------------------------------- */
+const char *fa_status_string(int status);
+/* Library build identification: "flagattn_b200 <n> sm_100a". */
+const char *fa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAGATTN_B200_H_ */

@@ -1,0 +1,182 @@
+"""GPU parity of flash_attention against the oracle, over the reference's own shape matrix
+(tests/flag_attn/test_flash_attention.py there) and the golden fixtures."""
+import os
+
+import pytest
+import torch
+
+import flagattention_b200 as fa
+import oracle
+from helpers import GOLDEN, assert_within_2x, make_qkv, max_diff
+
+pytestmark = pytest.mark.gpu
+
+FWD_SHAPES = [
+    (2, 4, 4, 512, 612, 128), (2, 4, 4, 1024, 1034, 64), (2, 4, 4, 2048, 2048, 32),
+    (2, 4, 4, 4096, 4096, 16), (2, 4, 4, 4001, 4001, 32), (2, 4, 4, 4001, 4096, 64),
+    (2, 4, 4, 4096, 4000, 128), (1, 2, 2, 8192, 8202, 16), (1, 2, 2, 8192, 8192, 32),
+    (2, 4, 2, 512, 612, 128), (2, 4, 1, 1024, 1034, 64), (2, 4, 2, 2048, 2048, 32),
+    (2, 4, 1, 4096, 4096, 16), (2, 4, 2, 4001, 4001, 32), (2, 4, 1, 4001, 4096, 64),
+    (2, 4, 2, 4096, 4000, 128), (1, 2, 1, 8192, 8202, 16), (1, 2, 1, 8192, 8192, 32),
+]
+BWD_EXTRA = [(2, 4, 4, 10006, 10, 128), (2, 4, 2, 10006, 10, 128)]
+SPLIT_SHAPES = [
+    (2, 4, 4, 1, 612, 128), (2, 4, 4, 1, 1034, 64), (2, 4, 4, 1, 2048, 32), (2, 4, 4, 1, 4096, 16),
+    (2, 4, 4, 1, 4001, 32), (2, 4, 4, 1, 4096, 64), (2, 4, 4, 2, 4000, 128), (1, 2, 2, 4, 8202, 16),
+    (1, 2, 2, 1, 8192, 32), (2, 4, 2, 1, 612, 128), (2, 4, 1, 1, 1034, 64), (2, 4, 2, 1, 2048, 32),
+    (2, 4, 1, 1, 4096, 16), (2, 4, 2, 1, 4001, 32), (2, 4, 1, 1, 4096, 64), (2, 4, 2, 2, 4000, 128),
+    (1, 2, 1, 4, 8202, 16), (1, 2, 1, 1, 8192, 32),
+]
+
+
+def _case_params(shapes):
+    out = []
+    for i, shp in enumerate(shapes):
+        for causal in (True, False):
+            for dtype in (torch.float16, torch.bfloat16):
+                layout = "BHTD" if (i + int(causal) + (dtype == torch.float16)) % 2 else "BTHD"
+                std = 1.0 + (i + 2 * int(causal)) % 4
+                out.append(pytest.param(*shp, causal, dtype, layout, std,
+                                        id=f"{'x'.join(map(str, shp))}-{'c' if causal else 'f'}-"
+                                           f"{str(dtype)[6:]}-{layout}-s{std:g}"))
+    return out
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,std", _case_params(FWD_SHAPES))
+def test_forward(B, Hq, Hk, M, N, D, causal, dtype, layout, std):
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", std, layout, seed=M + N + D)
+    o_ref = oracle.flash_attention(q, k, v, causal, upcast=True)
+    o_torch = oracle.flash_attention(q, k, v, causal, upcast=False)
+    o_hyp = fa.flash_attention(q, k, v, causal)
+    assert o_hyp.shape == q.shape and o_hyp.dtype == dtype
+    assert_within_2x(o_hyp, o_ref, o_torch, "o")
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,std", _case_params(SPLIT_SHAPES))
+def test_forward_split_kv_dispatch(B, Hq, Hk, M, N, D, causal, dtype, layout, std):
+    """Decode-shaped M makes flash_attention take the split-KV path (std 10 as in the reference)."""
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 10.0, layout, seed=M + N + D)
+    from flagattention_b200 import split_kv
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert split_kv.num_splits_herustic(B, Hq, M, N, 16, 128, sms, 128) > 1
+    o_ref, l_ref, _ = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True, upcast=True)
+    o_torch, l_torch, _ = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True, upcast=False)
+    o_hyp, l_hyp, *_ = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)
+    assert_within_2x(o_hyp, o_ref, o_torch, "o")
+    assert_within_2x(l_hyp, l_ref, l_torch, "log_normalizer")
+    o2 = fa.flash_attention_split_kv(q, k, v, causal)
+    assert_within_2x(o2, o_ref, o_torch, "o (standalone split-kv)")
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,std",
+                         _case_params([s for s in FWD_SHAPES if s[4] != 4000] +
+                                      [(2, 4, 4, 4096, 4001, 128), (2, 4, 2, 4096, 4001, 128)] + BWD_EXTRA))
+def test_backward(B, Hq, Hk, M, N, D, causal, dtype, layout, std):
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", std, layout, seed=M + N + D + 1)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o_ref = oracle.flash_attention(q, k, v, causal, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_torch = oracle.flash_attention(q, k, v, causal, upcast=False)
+    g_torch = torch.autograd.grad(o_torch, (q, k, v), do)
+    del o_ref, o_torch
+    o_hyp = fa.flash_attention(q, k, v, causal)
+    g_hyp = torch.autograd.grad(o_hyp, (q, k, v), do)
+    for name, h, r, t in zip(("dq", "dk", "dv"), g_hyp, g_ref, g_torch):
+        assert h.shape == r.shape and h.dtype == dtype
+        assert_within_2x(h, r, t, name)
+
+
+@pytest.mark.parametrize("B,H,M,N,D", [s[:2] + s[3:] for s in FWD_SHAPES[:6]] +
+                         [(2, 4, 4096, 4001, 128), (1, 2, 8192, 8202, 16), (1, 2, 8192, 8192, 32)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+def test_aux_outputs(B, H, M, N, D, dtype, causal):
+    layout = "BTHD" if (M + D) % 3 == 0 else "BHTD"
+    q, k, v, _ = make_qkv(B, H, H, M, N, D, dtype, "cuda", 1.0 + D % 3, layout, seed=D)
+    ref = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True,
+                                 return_total_attention=True, upcast=True)
+    tor = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True,
+                                 return_total_attention=True, upcast=False)
+    hyp = fa.flash_attention(q, k, v, causal, return_log_normalizer=True, return_total_attention=True)
+    assert len(hyp) == 5 and hyp[3] is None and hyp[4] is None
+    for name, h, r, t in zip(("o", "log_normalizer", "total_attention"), hyp[:3], ref, tor):
+        assert_within_2x(h, r, t, name)
+    only_l = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)
+    assert only_l[2] is None and torch.equal(only_l[1], hyp[1])
+
+
+def test_total_attention_gqa_and_standalone():
+    from flagattention_b200.total import total_attention
+    q, k, v, _ = make_qkv(2, 4, 2, 300, 333, 64, torch.bfloat16, "cuda", 1.0, "BHTD", seed=5)
+    ref = oracle.flash_attention(q, k, v, True, return_log_normalizer=True,
+                                 return_total_attention=True, upcast=True)
+    tor = oracle.flash_attention(q, k, v, True, return_log_normalizer=True,
+                                 return_total_attention=True, upcast=False)
+    o, L, tot, *_ = fa.flash_attention(q, k, v, True, return_log_normalizer=True,
+                                       return_total_attention=True)
+    assert tot.shape == (2, 4, 333)
+    assert_within_2x(tot, ref[2], tor[2], "total_attention")
+    tot2 = total_attention(q, k, L, causal=True)
+    assert torch.equal(tot, tot2)
+
+
+def test_empty_rows_give_zero_output_and_neg_inf_lse():
+    q, k, v, do = make_qkv(1, 2, 2, 100, 10, 64, torch.float16, "cuda", seed=3)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o, L, *_ = fa.flash_attention(q, k, v, True, return_log_normalizer=True)
+    assert torch.all(o[:, :, :90] == 0)
+    assert torch.all(torch.isinf(L[:, :, :90]) & (L[:, :, :90] < 0))
+    assert torch.isfinite(L[:, :, 90:]).all()
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+    assert torch.all(dq[:, :, :90] == 0)
+    assert torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
+
+
+def test_deterministic_and_stream_safe():
+    """No atomics anywhere: two runs are bitwise identical; a side stream gives the same bits."""
+    q, k, v, do = make_qkv(2, 4, 2, 777, 901, 128, torch.bfloat16, "cuda", seed=11)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    outs = []
+    for use_side in (False, False, True):
+        stream = torch.cuda.Stream() if use_side else torch.cuda.current_stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            o = fa.flash_attention(q, k, v, True)
+            g = torch.autograd.grad(o, (q, k, v), do)
+        stream.synchronize()
+        outs.append((o, *g))
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.equal(a, b)
+
+
+def test_golden_fixtures_on_gpu():
+    """Kernel vs the stored outputs of the reference's fp32 oracle (tests/golden/flash.pt)."""
+    cases = torch.load(os.path.join(GOLDEN, "flash.pt"))["cases"]
+    for c in cases:
+        q, k, v = (c[n].cuda().requires_grad_() for n in ("q", "k", "v"))
+        do = c["do"].cuda()
+        o, L, tot, *_ = fa.flash_attention(q, k, v, c["causal"], return_log_normalizer=True,
+                                           return_total_attention=True)
+        dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+        ref, tor = c["ref"], c["torch"]
+        for name, h in (("o", o), ("lse", L), ("tot", tot), ("dq", dq), ("dk", dk), ("dv", dv)):
+            assert_within_2x(h.cpu(), ref[name], tor[name], name)
+
+
+def test_cfg1_shape_fp16_against_fp32_golden():
+    """The CPU benchmark configuration run through the kernels in 16-bit: same inputs (rounded),
+    compared with the stored fp32 results at 16-bit resolution."""
+    c = torch.load(os.path.join(GOLDEN, "flash.pt"))["cfg1"]
+    gen = torch.Generator().manual_seed(c["seed"])
+    q, k, v, do = (torch.randn(c["shape"], generator=gen, dtype=torch.float32) for _ in range(4))
+    qh, kh, vh, doh = (t.half().cuda() for t in (q, k, v, do))
+    qh.requires_grad_(), kh.requires_grad_(), vh.requires_grad_()
+    o, L, tot, *_ = fa.flash_attention(qh, kh, vh, True, sm_scale=c["sm_scale"],
+                                       return_log_normalizer=True, return_total_attention=True)
+    dq, dk, dv = torch.autograd.grad(o, (qh, kh, vh), doh)
+    assert max_diff(L.cpu(), c["lse"]) < 2e-2
+    assert max_diff(tot.cpu(), c["tot"]) < 2e-2
+    h = c["head"]
+    for got, name in ((o, "o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert max_diff(got[h].cpu(), c[name]) < 3e-2, name

@@ -1,0 +1,121 @@
+"""Host-side logic that needs no GPU: split heuristics, partition planning, layout normalisation,
+operator argument checks."""
+import math
+
+import pytest
+import torch
+
+import flagattention_b200 as fa
+from flagattention_b200 import _C, paged, split_kv
+
+
+def _heuristic_python(B, H, M, N, BLOCK_M, BLOCK_N, num_sms, max_splits):
+    """Independent restatement of the reference rule (src/flag_attn/split_kv.py:234-262 there)."""
+    cdiv = lambda a, b: (a + b - 1) // b
+    blocks = B * H * cdiv(M, BLOCK_M)
+    if blocks >= 0.8 * num_sms:
+        return 1
+    n_blocks = cdiv(N, BLOCK_N)
+
+    def ok(s):
+        per = cdiv(n_blocks, s)
+        return s == 1 or per * s - n_blocks < per
+
+    def eff(s):
+        waves = blocks * s / num_sms
+        return waves / math.ceil(waves)
+
+    plans = [(s, eff(s)) for s in range(1, min(num_sms, n_blocks, max_splits) + 1) if ok(s)]
+    best = max([e for _, e in plans], default=0.0)
+    for s, e in plans:
+        if e >= 0.85 * best:
+            return s
+    return 1
+
+
+@pytest.mark.parametrize("sms", [108, 132, 148])
+def test_split_heuristic_matches_restatement(built_lib, sms):
+    for B, H, M, N in [(2, 4, 1, 612), (2, 4, 1, 4096), (1, 2, 4, 8202), (4, 32, 4096, 4096),
+                       (1, 1, 1, 524288), (2, 4, 2, 4000), (1, 2, 1, 8192), (1, 16, 3, 100),
+                       (8, 8, 16, 2048), (1, 1, 17, 129)]:
+        assert split_kv.num_splits_herustic(B, H, M, N, 16, 128, sms, 128) == \
+            _heuristic_python(B, H, M, N, 16, 128, sms, 128)
+
+
+def test_paged_partition_plan():
+    plan = paged.plan_partitions
+    # north-star decode config: explicit 64 splits of a 32768 context -> 512-token partitions
+    assert plan(64, 8, 16, 32768, 64, 148) == (64, 512)
+    # automatic: few CTAs -> 256-token partitions
+    assert plan(1, 8, 16, 4096, 0, 148) == (16, 256)
+    # automatic: short context or huge blocks -> one pass
+    assert plan(1, 8, 16, 512, 0, 148) == (1, 0)
+    assert plan(1, 8, 256, 4096, 0, 148) == (1, 0)
+    # automatic: many CTAs and short context -> one pass; long context -> partitions
+    assert plan(64, 8, 16, 2048, 0, 148) == (1, 0)
+    assert plan(64, 8, 16, 4096, 0, 148) == (16, 256)
+    # explicit single split
+    assert plan(16, 8, 16, 2048, 1, 148) == (1, 0)
+    # explicit odd split counts round the partition up to a power of two
+    assert plan(16, 8, 16, 2048, 3, 148) == (3, 1024)
+    assert plan(16, 8, 16, 2048, 6, 148) == (6, 512)
+    assert plan(1, 12, 16, 2, 0, 148) == (1, 0)
+
+
+def test_kernel_ready_layouts():
+    x = torch.zeros(2, 4, 32, 64, dtype=torch.float16)
+    assert _C.kernel_ready(x) is x
+    bthd = torch.zeros(2, 32, 4, 64, dtype=torch.float16).transpose(1, 2)
+    assert _C.kernel_ready(bthd) is bthd                       # arbitrary outer strides are fine
+    inner = torch.zeros(2, 4, 64, 32, dtype=torch.float16).transpose(2, 3)
+    assert _C.kernel_ready(inner).is_contiguous()              # inner stride must be 1
+    odd = torch.zeros(2, 4, 32, 72, dtype=torch.float16)[..., 4:68]
+    assert _C.kernel_ready(odd).is_contiguous()                # rows must start 16-byte aligned
+    t = _C.tensor4(bthd)
+    assert (t.stride_b, t.stride_h, t.stride_l) == (32 * 4 * 64, 64, 4 * 64)
+
+
+def test_operator_argument_errors_match_reference_convention():
+    """Shape violations raise AssertionError before touching the GPU, as in the reference
+    (src/flag_attn/flash.py:26-35, src/flag_attn/piecewise.py:29-31, src/flag_attn/paged.py:31-32)."""
+    q = torch.zeros(1, 4, 8, 48, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        fa.flash_attention(q, q, q)                            # head_dim 48
+    q = torch.zeros(1, 4, 8, 64, dtype=torch.float16)
+    k = torch.zeros(1, 3, 8, 64, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        fa.flash_attention(q, k, k)                            # 4 % 3 != 0
+    with pytest.raises(AssertionError):
+        fa.flash_attention(q, q, q[..., :32])                  # mismatched head_dim
+    with pytest.raises(AssertionError):
+        fa.piecewise_attention(q, q, q, q[..., :32], q, 4)
+    with pytest.raises(AssertionError):
+        fa.paged_attention(torch.zeros(2, 8, 24, dtype=torch.float16),
+                           torch.zeros(4, 2, 16, 24, dtype=torch.float16),
+                           torch.zeros(4, 2, 16, 24, dtype=torch.float16),
+                           torch.ones(2, dtype=torch.int32), torch.zeros(2, 1, dtype=torch.int32),
+                           1.0, 16)                            # head_size 24
+    with pytest.raises(AssertionError):
+        fa.paged_attention(torch.zeros(2, 8, 32, dtype=torch.float16),
+                           torch.zeros(4, 2, 8, 32, dtype=torch.float16),
+                           torch.zeros(4, 2, 8, 32, dtype=torch.float16),
+                           torch.ones(2, dtype=torch.int32), torch.zeros(2, 1, dtype=torch.int32),
+                           1.0, 8)                             # group > 1 needs block_size >= 16
+
+
+def test_public_api_surface():
+    for name in ("flash_attention", "piecewise_attention", "paged_attention",
+                 "flash_attention_split_kv", "testing"):
+        assert hasattr(fa, name)
+    for name in ("flash_attention", "piecewise_attention", "paged_attention"):
+        assert hasattr(fa.testing, name)
+    import inspect
+    sig = inspect.signature(fa.flash_attention)
+    assert list(sig.parameters) == ["q", "k", "v", "causal", "sm_scale", "dropout_p",
+                                    "return_log_normalizer", "return_total_attention",
+                                    "return_seed_offset"]
+    sig = inspect.signature(fa.piecewise_attention)
+    assert list(sig.parameters) == ["q1", "k1", "q2", "k2", "v", "dist_threshold", "causal", "sm_scale"]
+    sig = inspect.signature(fa.paged_attention)
+    assert list(sig.parameters) == ["query", "key_cache", "value_cache", "context_lens",
+                                    "block_tables", "attn_scale", "max_context_len", "num_splits"]

@@ -33,7 +33,7 @@ def _forward(q, k, v, causal, sm_scale):
     B, H, M, D = q.shape
     N, Hk = k.shape[2], k.shape[1]
     lib = _C.load()
-    o = torch.empty_like(q) if q.is_contiguous() else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     L = torch.empty((B, H, M), device=q.device, dtype=torch.float32)
     shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
     tq, tk, tv, to = _C.tensor4(q), _C.tensor4(k), _C.tensor4(v), _C.tensor4(o)
@@ -54,6 +54,44 @@ def _total_attention(q, k, L, causal, sm_scale):
                                 _C.fptr(tot), _C.stream_ptr(q.device))
     _C.check(st, "fa_total_attention")
     return tot
+
+
+def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None):
+    """Launches delta, dK/dV and dQ. `mark(name)`, when given, is called before the first launch
+    and after each one (the benchmark records CUDA events there)."""
+    B, H, M, D = q.shape
+    N, Hk = k.shape[2], k.shape[1]
+    lib = _C.load()
+    do = _C.kernel_ready(do)
+    with torch.cuda.device(q.device):
+        stream = _C.stream_ptr(q.device)
+        shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
+        delta = torch.empty_like(L)
+        # dk / dv come out with Hk heads: the group sum is done in the kernel
+        dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=q.device)
+        dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=q.device)
+        dq = torch.empty((B, H, M, D), dtype=q.dtype, device=q.device)
+        tq, tk, tv, to, tdo = (_C.tensor4(x) for x in (q, k, v, o, do))
+        tdk, tdv, tdq = _C.tensor4(dk), _C.tensor4(dv), _C.tensor4(dq)
+        if mark:
+            mark("start")
+        st = lib.fa_flash_bwd_delta(_C.byref(shape), _C.byref(to), _C.byref(tdo),
+                                    _C.fptr(delta), stream)
+        _C.check(st, "fa_flash_bwd_delta")
+        if mark:
+            mark("delta")
+        st = lib.fa_flash_bwd_dkdv(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
+                                   _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdk),
+                                   _C.byref(tdv), stream)
+        _C.check(st, "fa_flash_bwd_dkdv")
+        if mark:
+            mark("dkdv")
+        st = lib.fa_flash_bwd_dq(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
+                                 _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdq), stream)
+        _C.check(st, "fa_flash_bwd_dq")
+        if mark:
+            mark("dq")
+    return dq, dk, dv
 
 
 class FlashAttention(torch.autograd.Function):
@@ -103,36 +141,7 @@ class FlashAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, *ignored):
         q, k, v, o, L = ctx.saved_tensors
-        sm_scale, causal = ctx.sm_scale, ctx.causal
-        B, H, M, D = q.shape
-        N, Hk = k.shape[2], k.shape[1]
-        lib = _C.load()
-        do = _C.kernel_ready(do)
-
-        with torch.cuda.device(q.device):
-            stream = _C.stream_ptr(q.device)
-            shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
-            delta = torch.empty_like(L)
-            tq, tk, tv, to, tdo = (_C.tensor4(x) for x in (q, k, v, o, do))
-            st = lib.fa_flash_bwd_delta(_C.byref(shape), _C.byref(to), _C.byref(tdo),
-                                        _C.fptr(delta), stream)
-            _C.check(st, "fa_flash_bwd_delta")
-
-            # dk / dv come out with Hk heads: the group sum is done in the kernel
-            dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=q.device)
-            dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=q.device)
-            tdk, tdv = _C.tensor4(dk), _C.tensor4(dv)
-            st = lib.fa_flash_bwd_dkdv(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
-                                       _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdk),
-                                       _C.byref(tdv), stream)
-            _C.check(st, "fa_flash_bwd_dkdv")
-
-            dq = torch.empty((B, H, M, D), dtype=q.dtype, device=q.device)
-            tdq = _C.tensor4(dq)
-            st = lib.fa_flash_bwd_dq(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
-                                     _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdq),
-                                     stream)
-            _C.check(st, "fa_flash_bwd_dq")
+        dq, dk, dv = _backward(q, k, v, o, L, do, ctx.causal, ctx.sm_scale)
         return dq, dk, dv, None, None, None, None, None, None
 
 

@@ -1,5 +1,22 @@
-// Status strings and build identification.
+// Status strings, build identification and the device status word.
+#include <cuda_runtime.h>
+
 #include "flagattn_b200.h"
+
+namespace fa {
+
+// Written by a kernel whose bounded wait ran out (the code says which wait);
+// zero in normal operation.  One word per device, inside the library image.
+__device__ int g_device_status[4];
+
+// Device address of the status word of the current device, or null.
+int *device_status_word() {
+  void *ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
+  return static_cast<int *>(ptr);
+}
+
+}  // namespace fa
 
 extern "C" const char *fa_status_string(int status) {
   switch (status) {
@@ -15,3 +32,17 @@ extern "C" const char *fa_status_string(int status) {
 }
 
 extern "C" const char *fa_version(void) { return "flagattn_b200 1 sm_100a"; }
+
+extern "C" int fa_device_status(int32_t *out, int32_t clear) {
+  if (!out) return FA_ERR_BAD_ARG;
+  int *word = fa::device_status_word();
+  if (!word) return FA_ERR_LAUNCH;
+  if (cudaMemcpy(out, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return FA_ERR_LAUNCH;
+  if (clear && *out != 0) {
+    int zero = 0;
+    if (cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess)
+      return FA_ERR_LAUNCH;
+  }
+  return FA_OK;
+}

@@ -62,6 +62,11 @@ static FwdParams make_fwd_params(const fa_flash_shape *s, const fa_tensor4 *q, c
   return p;
 }
 
+namespace tc {
+int flash_fwd_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                 const fa_tensor4 *v, const fa_tensor4 *o, float *lse, cudaStream_t stream);
+}
+
 }  // namespace fa
 
 using namespace fa;
@@ -71,6 +76,9 @@ extern "C" int fa_flash_fwd(const fa_flash_shape *s, const fa_tensor4 *q, const 
   if (int st = validate_shape(s)) return st;
   if (int st = validate_tensors({q, k, v, o})) return st;
   if (!lse) return FA_ERR_BAD_ARG;
+  // head_dim 64 / 128 run on tcgen05; everything else on the shape-generic kernel
+  const int tc_status = tc::flash_fwd_tc(s, q, k, v, o, lse, static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   FwdParams p = make_fwd_params(s, q, k, v);
   p.o = o->ptr, p.so = strides_of(o), p.lse = lse;
   return dispatch_dtype_d(s->dtype, s->D, FwdLaunch{p, static_cast<cudaStream_t>(stream)});

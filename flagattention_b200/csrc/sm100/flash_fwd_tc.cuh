@@ -1,0 +1,318 @@
+// flash_attention forward on the 5th-generation tensor cores (tcgen05) for
+// head_dim 64 and 128.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the visible keys
+// in tiles of 64.  Warp roles:
+//   warp 0      TMA producer: Q once, then K and V tiles through two 2-stage rings
+//   warp 1      MMA issuer (one thread): S = Q K^T into a double-buffered TMEM
+//               tile, O += P V with P read back from TMEM
+//   warps 2..5  softmax, one thread per query row: tcgen05.ld of its S row,
+//               running max / sum, P written over S in TMEM as 16-bit pairs,
+//               lazy rescale of the O accumulator, final normalise + store
+// S(j+1) is issued before P(j) V(j), so the tensor pipe computes the next
+// scores while the softmax warps work on the current tile; two CTAs per SM
+// (256 of the 512 TMEM columns each) overlap each other's remaining gaps.
+#pragma once
+
+#include "../attn_params.cuh"
+#include "tc_common.cuh"
+
+namespace fa {
+namespace tc {
+
+struct FwdTcParams {
+  void *o;
+  float *lse;
+  Strides so;
+  int B, H, Hk, M, N;
+  int causal;
+  float sm_scale;
+  int *status;
+};
+
+template <int D>
+struct FwdTcCfg {
+  static constexpr int BM = 128, BN = 64;
+  static constexpr int KSUB = D / 64;                 // 64-column (128-byte) sub-tiles per row
+  static constexpr int kQBytes = BM * D * 2;
+  static constexpr int kKVBytes = BN * D * 2;
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQBytes;                  // 2 stages
+  static constexpr int kV = kK + 2 * kKVBytes;        // 2 stages
+  static constexpr int kBars = kV + 2 * kKVBytes;     // 16 mbarriers
+  static constexpr int kMisc = kBars + 16 * 8;        // tmem base, abort flag
+  static constexpr int kTotal = kMisc + 16 + 1024;    // + slack to align the base to 1024 bytes
+  static constexpr int kTmemCols = 256;               // S0 | S1 | O, rounded to a power of two
+  static constexpr int kColS0 = 0, kColS1 = 64, kColO = 128;
+  static constexpr int kThreads = 192;
+};
+
+enum FwdBar { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, P_READY = 11,
+              PV_DONE = 13 };
+
+template <typename T, int D>
+__global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
+    flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                        const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const FwdTcParams p) {
+  using C = FwdTcCfg<D>;
+  constexpr int BM = C::BM, BN = C::BN, KSUB = C::KSUB;
+  extern __shared__ uint8_t smem_unaligned[];
+  const uint32_t smem = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_unaligned + (smem - smem_u32(smem_unaligned));
+  auto bar = [&](int i) { return smem + C::kBars + i * 8; };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + C::kMisc);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + C::kMisc + 8);
+  const AbortCtx actx{abort_flag, p.status};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mb = gridDim.x - 1 - blockIdx.x;  // heaviest causal tiles first
+  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  const int hk = h / (p.H / p.Hk);
+  const int m0 = mb * BM;
+  const int p_seq = p.N - p.M;
+  int n_hi = p.N;
+  if (p.causal) n_hi = min(n_hi, p_seq + m0 + BM);
+  const int T_tiles = n_hi > 0 ? (n_hi + BN - 1) / BN : 0;
+
+  // a wait that ran out earlier (this launch or a previous one) poisons the device status word:
+  // do no work until the host has read and cleared it
+  if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(K_FULL + s), 1);
+      mbar_init(bar(K_FREE + s), 1);
+      mbar_init(bar(V_FULL + s), 1);
+      mbar_init(bar(V_FREE + s), 1);
+      mbar_init(bar(S_FULL + s), 1);
+      mbar_init(bar(P_READY + s), 128);
+      mbar_init(bar(PV_DONE + s), 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem + C::kMisc, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && T_tiles > 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      mbar_expect_tx(bar(Q_FULL), C::kQBytes);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kQ + s * BM * 128, &map_q, bar(Q_FULL), s * 64, m0, h, b);
+      int issued_k = 0, issued_v = 0;
+      bool ok = true;
+      for (int j = 0; j < T_tiles && ok; ++j) {
+        const int st = j & 1, ph = (j >> 1) & 1, n0 = j * BN;
+        ok = mbar_wait(bar(K_FREE + st), ph ^ 1, actx, 101);
+        if (!ok) break;
+        mbar_expect_tx(bar(K_FULL + st), C::kKVBytes);
+        for (int s = 0; s < KSUB; ++s)
+          tma_load_4d(smem + C::kK + st * C::kKVBytes + s * BN * 128, &map_k, bar(K_FULL + st),
+                      s * 64, n0, hk, b);
+        ++issued_k;
+        ok = mbar_wait(bar(V_FREE + st), ph ^ 1, actx, 102);
+        if (!ok) break;
+        mbar_expect_tx(bar(V_FULL + st), C::kKVBytes);
+        for (int s = 0; s < KSUB; ++s)
+          tma_load_4d(smem + C::kV + st * C::kKVBytes + s * BN * 128, &map_v, bar(V_FULL + st),
+                      s * 64, n0, hk, b);
+        ++issued_v;
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA gives its shared memory back
+        const long long t0 = clock64();
+        for (int i = max(0, issued_k - 2); i < issued_k; ++i)
+          while (!mbar_try_wait(bar(K_FULL + (i & 1)), (i >> 1) & 1) && clock64() - t0 < 2000000) {}
+        for (int i = max(0, issued_v - 2); i < issued_v; ++i)
+          while (!mbar_try_wait(bar(V_FULL + (i & 1)), (i >> 1) & 1) && clock64() - t0 < 2000000) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0 && T_tiles > 0) {
+      constexpr uint32_t idesc_s = instr_desc_f16(BM, BN, TcElem<T>::kFormat, 0, 0);
+      constexpr uint32_t idesc_pv = instr_desc_f16(BM, D, TcElem<T>::kFormat, 0, 1);
+      bool ok = mbar_wait(bar(Q_FULL), 0, actx, 201);
+      auto issue_pv = [&](int i) -> bool {
+        const int st = i & 1, ph = (i >> 1) & 1;
+        if (!mbar_wait(bar(V_FULL + st), ph, actx, 203)) return false;
+        if (!mbar_wait(bar(P_READY + st), ph, actx, 204)) return false;
+        tc_fence_after();
+        const uint32_t vbase = smem + C::kV + st * C::kKVBytes;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t bd = smem_desc_sw128(vbase + kk * 16 * 128, BN * 128, 1024);
+          mma_ts(tmem + C::kColO, tmem + (st ? C::kColS1 : C::kColS0) + kk * 8, bd, idesc_pv,
+                 (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(bar(PV_DONE + st));
+        mma_commit(bar(V_FREE + st));
+        return true;
+      };
+      for (int j = 0; j < T_tiles && ok; ++j) {
+        const int st = j & 1, ph = (j >> 1) & 1;
+        ok = mbar_wait(bar(K_FULL + st), ph, actx, 202);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t kbase = smem + C::kK + st * C::kKVBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t ad =
+              smem_desc_sw128(smem + C::kQ + (k / 4) * BM * 128 + (k % 4) * 32, 0, 1024);
+          const uint64_t bd = smem_desc_sw128(kbase + (k / 4) * BN * 128 + (k % 4) * 32, 0, 1024);
+          mma_ss(tmem + (st ? C::kColS1 : C::kColS0), ad, bd, idesc_s, k > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(S_FULL + st));
+        mma_commit(bar(K_FREE + st));
+        if (j >= 1) ok = issue_pv(j - 1);
+      }
+      if (ok) ok = issue_pv(T_tiles - 1);
+      // the last commit's arrive must land before this CTA's shared memory is given back
+      if (ok) mbar_wait(bar(V_FREE + ((T_tiles - 1) & 1)), ((T_tiles - 1) >> 1) & 1, actx, 205);
+    }
+  } else {
+    // ------------------------------ softmax warps -----------------------------
+    const int slice = warp & 3;
+    const int row_in_tile = slice * 32 + lane;
+    const int row = m0 + row_in_tile;
+    const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
+    const float qk_scale = p.sm_scale * kLog2e;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < T_tiles; ++j) {
+      const int st = j & 1, ph = (j >> 1) & 1, n0 = j * BN;
+      ok = mbar_wait(bar(S_FULL + st), ph, actx, 301);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t scol = tlane + (st ? C::kColS1 : C::kColS0);
+      uint32_t raw[2][32];
+      tmem_ld32(scol, raw[0]);
+      tmem_ld32(scol + 32, raw[1]);
+      tmem_wait_ld();
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < BN; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
+
+      const bool need_mask = (n0 + BN > p.N) || (p.causal && (n0 + BN - 1 > m0 + p_seq));
+      if (need_mask) {
+        int limit = p.N - n0;
+        if (p.causal) limit = min(limit, row + p_seq - n0 + 1);
+#pragma unroll
+        for (int c = 0; c < BN; ++c)
+          if (c >= limit) s[c] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int c = 1; c < BN; ++c) mx = fmaxf(mx, s[c]);
+      const float m_new = fmaxf(m_used, mx);
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = (m_new - m_used) * qk_scale > 8.f;
+        if (__any_sync(0xffffffffu, need)) {
+          const int pj = j - 1;
+          ok = mbar_wait(bar(PV_DONE + (pj & 1)), (pj >> 1) & 1, actx, 302);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          float alpha = 1.f;
+          if (need) {
+            alpha = ex2((m_used - m_new) * qk_scale);
+            l *= alpha;
+            m_used = m_new;
+          }
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(tlane + C::kColO + c * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st32(tlane + C::kColO + c * 32, ov);
+          }
+          tmem_wait_st();
+        }
+      }
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      const float neg_ms = -m_eff * qk_scale;
+      uint32_t pk[BN / 2];
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN; c += 2) {
+        const float p0 = ex2(fmaf(s[c], qk_scale, neg_ms));
+        const float p1 = ex2(fmaf(s[c + 1], qk_scale, neg_ms));
+        rs += p0 + p1;
+        pk[c >> 1] = TcElem<T>::pack(p0, p1);
+      }
+      l += rs;
+      tmem_st32(scol, reinterpret_cast<const uint32_t(&)[32]>(pk));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(P_READY + st));
+    }
+
+    // epilogue: O / l -> global, log-normaliser
+    if (ok && T_tiles > 0) {
+      const int lj = T_tiles - 1;
+      ok = mbar_wait(bar(PV_DONE + (lj & 1)), (lj >> 1) & 1, actx, 303);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T *orow = row_ptr_mut<T>(p.o, p.so, b, h, row);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ov[32];
+        if (T_tiles > 0) {
+          tmem_ld32(tlane + C::kColO + c * 32, ov);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (row < p.M) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = TcElem<T>::pack(__uint_as_float(ov[8 * i + 0]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+            v.y = TcElem<T>::pack(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+            v.z = TcElem<T>::pack(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+            v.w = TcElem<T>::pack(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4 *>(orow + c * 32 + i * 8) = v;
+          }
+        }
+      }
+      if (row < p.M) {
+        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+        p.lse[((int64_t)b * p.H + h) * p.M + row] =
+            l > 0.f ? m_eff * p.sm_scale + logf(l) : -INFINITY;
+      }
+    }
+  }
+
+  // ------------------------------ teardown -----------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+}  // namespace tc
+}  // namespace fa

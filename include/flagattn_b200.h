@@ -198,6 +198,14 @@ int fa_paged_trace_blocks(const fa_paged_args *a, int64_t *visited, int32_t max_
                           void *stream);
 
 /* ---------------------------------------------------------------------- */
+/* Health check of the tensor-core kernels.  Every wait inside them is bounded
+ * (about a second); a wait that runs out stores a code naming the wait in a
+ * per-device status word, and the kernel tears down and returns instead of
+ * hanging.  This call synchronises with the device, copies the word to *out
+ * (0 = healthy) and optionally clears it.  The reference has no counterpart:
+ * its Triton kernels contain no waits (src/flag_attn/flash.py:325-489). */
+int fa_device_status(int32_t *out, int32_t clear);
+
 const char *fa_status_string(int status);
 /* Library build identification: "flagattn_b200 <n> sm_100a". */
 const char *fa_version(void);

@@ -83,6 +83,16 @@ struct TotalLaunch {
   }
 };
 
+namespace tc {
+int flash_bwd_dq_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                    const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                    const float *delta, const fa_tensor4 *dq, cudaStream_t stream);
+int flash_bwd_dkdv_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                      const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                      const float *delta, const fa_tensor4 *dk, const fa_tensor4 *dv,
+                      cudaStream_t stream);
+}  // namespace tc
+
 }  // namespace fa
 
 using namespace fa;
@@ -115,6 +125,10 @@ extern "C" int fa_flash_bwd_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, c
   if (int st = validate_shape(s)) return st;
   if (int st = validate_tensors({q, k, v, d_o, dk, dv})) return st;
   if (!lse || !delta) return FA_ERR_BAD_ARG;
+  // head_dim 64 / 128 run on tcgen05; everything else on the shape-generic kernel
+  const int tc_status = tc::flash_bwd_dkdv_tc(s, q, k, v, d_o, lse, delta, dk, dv,
+                                              static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   BwdParams p = make_bwd(s, q, k, v, d_o, lse, delta);
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
   return dispatch_dtype_d(s->dtype, s->D, DkdvLaunch<false>{p, static_cast<cudaStream_t>(stream)});
@@ -126,6 +140,9 @@ extern "C" int fa_flash_bwd_dq(const fa_flash_shape *s, const fa_tensor4 *q, con
   if (int st = validate_shape(s)) return st;
   if (int st = validate_tensors({q, k, v, d_o, dq})) return st;
   if (!lse || !delta) return FA_ERR_BAD_ARG;
+  const int tc_status =
+      tc::flash_bwd_dq_tc(s, q, k, v, d_o, lse, delta, dq, static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   BwdParams p = make_bwd(s, q, k, v, d_o, lse, delta);
   p.dq = dq->ptr, p.sdq = strides_of(dq);
   return dispatch_dtype_d(s->dtype, s->D, DqLaunch<false>{p, static_cast<cudaStream_t>(stream)});

@@ -180,3 +180,41 @@ def test_cfg1_shape_fp16_against_fp32_golden():
     h = c["head"]
     for got, name in ((o, "o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
         assert max_diff(got[h].cpu(), c[name]) < 3e-2, name
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D", [(2, 4, 2, 512, 612, 128), (2, 4, 1, 1024, 1034, 64),
+                                           (2, 4, 4, 4001, 4096, 64), (2, 4, 2, 4096, 4001, 128),
+                                           (2, 4, 2, 10006, 10, 128)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_generic_kernels_at_tensor_core_head_dims(B, Hq, Hk, M, N, D, causal, monkeypatch):
+    """head_dim 64/128 normally run on the tcgen05 kernels; FLAGATTN_B200_GENERIC=1 routes them to
+    the shape-generic kernels, which must meet the same bar (and agree with the tcgen05 ones)."""
+    dtype = torch.bfloat16 if causal else torch.float16
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 1.0, "BHTD", seed=M + D)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o_ref, l_ref, _ = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_tor, l_tor, _ = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True, upcast=False)
+    g_tor = torch.autograd.grad(o_tor, (q, k, v), do)
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("FLAGATTN_B200_GENERIC", mode)
+        o, L, *_ = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)
+        g = torch.autograd.grad(o, (q, k, v), do)
+        assert_within_2x(o, o_ref, o_tor, f"o generic={mode}")
+        assert_within_2x(L, l_ref, l_tor, f"lse generic={mode}")
+        for name, h, r, t in zip(("dq", "dk", "dv"), g, g_ref, g_tor):
+            assert_within_2x(h, r, t, f"{name} generic={mode}")
+        results[mode] = (o, L, *g)
+    for a, b_ in zip(results["0"], results["1"]):
+        fin = torch.isfinite(a.float())
+        assert max_diff(a[fin], b_[fin]) <= 4 * 2 ** -8 * max(1.0, a[fin].float().abs().max().item())
+
+
+def test_device_status_word_is_clean():
+    """Every wait in the tcgen05 kernels is bounded; none of them may have run out in this process."""
+    import ctypes
+    from flagattention_b200 import _C
+    out = ctypes.c_int32(-1)
+    assert _C.load().fa_device_status(ctypes.byref(out), 0) == 0
+    assert out.value == 0

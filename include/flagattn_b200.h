@@ -190,6 +190,29 @@ int fa_paged_reduce(const fa_paged_args *a, void *stream);
 /* Bytes needed for part_out + part_max + part_sum (host-only helper). */
 int64_t fa_paged_workspace_bytes(const fa_paged_args *a);
 
+/* Partitioned paged decode that needs no workspace from the caller.  It has no
+ * counterpart in the reference, whose wrapper always allocates its split-KV
+ * buffers with torch.  It exists for hosts that cannot allocate: a server that
+ * handed all free HBM to its KV-cache pool, or a decode loop that must never
+ * enter the CUDA allocator.  The partial outputs and softmax statistics live
+ * in a fixed FA_PAGED_NOALLOC_SCRATCH_BYTES array inside the library image
+ * (held by every GPU that loads the library, until the process exits).
+ *   - `a->partition_size` must be > 0; `a->part_out/part_max/part_sum` are
+ *     ignored; inputs and `a->out` are the caller's as usual.
+ *   - Requests whose workspace (fa_paged_workspace_bytes) exceeds the array
+ *     return FA_ERR_TOO_LARGE: at head_size 128 that is more than 32768
+ *     (sequence, query head, partition) slots.
+ *   - Runs the decode kernel and the reducer on `stream`.  Calls cudaMalloc,
+ *     cudaFree or any other allocating routine never.  The first call on each
+ *     device resolves the array's device address (cudaGetSymbolAddress); make
+ *     that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps whatever the
+ *     previous call left in it (every slot read is rewritten first, so no
+ *     clearing is needed).  Two calls whose kernels overlap on the GPU (for
+ *     example on different streams) race on it: serialise them. */
+#define FA_PAGED_NOALLOC_SCRATCH_BYTES 17039360 /* 32768 slots x (128 fp32 + 2 fp32) */
+int fa_paged_attention_noalloc(const fa_paged_args *a, void *stream);
+
 /* Test hook for "integer block-table indexing is bit-exact": writes, for
  * every (seq, logical block < ceil(context_len / block_size)), the physical
  * block id the decode kernel would gather from into visited[seq, block]

@@ -84,26 +84,51 @@ __global__ void __launch_bounds__(PagedCfg<D>::kWarps * 32) paged_decode_kernel(
   const T *kc = reinterpret_cast<const T *>(a.key_cache) + (int64_t)hk * a.kv_stride_h;
   const T *vc = reinterpret_cast<const T *>(a.value_cache) + (int64_t)hk * a.kv_stride_h;
 
+  // Per-lane constants of the gather.  In every 16-token group this lane copies the 16-byte
+  // chunk `ch` of rows c * RPC + lane_r (c = 0..NC-1), for K and for V, so the shared-memory
+  // offsets are fixed and the global address only advances by RPC rows per step.
+  constexpr int NC = 16 * CPR / 32;  // copy steps per lane per group
+  constexpr int RPC = 16 / NC;       // rows covered per step
+  const int lane_r = lane / CPR, ch = lane % CPR;
+  uint32_t dst_off[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) dst_off[c] = Tile<D>::offset(c * RPC + lane_r, ch);
+  const int64_t lane_src = (int64_t)lane_r * a.kv_stride_t + ch * 8;
+  const int64_t c_step = (int64_t)RPC * a.kv_stride_t;
+  const int64_t v_minus_k = vc - kc;
+  const int bs_shift = (BS & (BS - 1)) == 0 ? 31 - __clz(BS) : -1;
+
   auto issue = [&](int i) {  // i-th group of this warp -> stage i % NS
     const int tok0 = t_begin + (warp + i * NW) * 16;
     const uint32_t st = ring + (i % NS) * C::kStageBytes;
-    int64_t pb_uniform = 0;
-    if (group_in_block) pb_uniform = phys_block<IdxT>(a.block_tables, a.bt_stride_s, seq, tok0 / BS);
+    if (group_in_block) {
+      // the whole group lies in one physical block: one table lookup, then pointer increments
+      const int lb = bs_shift >= 0 ? tok0 >> bs_shift : tok0 / BS;
+      const int in_blk = tok0 - lb * BS;
+      const int64_t pb = phys_block<IdxT>(a.block_tables, a.bt_stride_s, seq, lb);
+      const T *src = kc + pb * a.kv_stride_b + (int64_t)in_blk * a.kv_stride_t + lane_src;
+      const int rows_left = t_end - tok0 - lane_r;  // row c*RPC + lane_r exists iff c*RPC < rows_left
 #pragma unroll
-    for (int c = 0; c < 16 * CPR / 32; ++c) {
-      const int idx = lane + c * 32;
-      const int r = idx / CPR, ch = idx % CPR;
-      const int tok = tok0 + r;
-      const bool ok = tok < t_end;
-      int64_t off = 0;
-      if (ok) {
-        const int64_t pb = group_in_block
-                               ? pb_uniform
-                               : phys_block<IdxT>(a.block_tables, a.bt_stride_s, seq, tok / BS);
-        off = pb * a.kv_stride_b + (int64_t)(tok % BS) * a.kv_stride_t + ch * 8;
+      for (int c = 0; c < NC; ++c) {
+        const bool ok = c * RPC < rows_left;
+        const T *sk = ok ? src : kc;
+        cp_async16(st + dst_off[c], sk, ok);
+        cp_async16(st + C::kGroupBytes + dst_off[c], sk + v_minus_k, ok);
+        src += c_step;
       }
-      cp_async16(st + Tile<D>::offset(r, ch), kc + off, ok);
-      cp_async16(st + C::kGroupBytes + Tile<D>::offset(r, ch), vc + off, ok);
+    } else {
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int tok = tok0 + c * RPC + lane_r;
+        const bool ok = tok < t_end;
+        int64_t off = 0;
+        if (ok) {
+          const int64_t pb = phys_block<IdxT>(a.block_tables, a.bt_stride_s, seq, tok / BS);
+          off = pb * a.kv_stride_b + (int64_t)(tok % BS) * a.kv_stride_t + ch * 8;
+        }
+        cp_async16(st + dst_off[c], kc + off, ok);
+        cp_async16(st + C::kGroupBytes + dst_off[c], vc + off, ok);
+      }
     }
   };
 
@@ -155,26 +180,41 @@ __global__ void __launch_bounds__(PagedCfg<D>::kWarps * 32) paged_decode_kernel(
         const int tok = tok0 + j * 8 + 2 * t4 + (e & 1);
         s[j][e] = (tail && tok >= t_end) ? -INFINITY : s[j][e] * qk_scale;
       }
+    // Running maximum with lazy rescaling: the accumulators are only rescaled when some row's
+    // maximum grew by more than 2^8 (scores are already in the base-2 domain); otherwise the
+    // stale maximum stays the reference point and P simply ranges up to 2^8.
+    float m_new[2];
+    bool need = false;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
       mx = quad_max(mx);
-      const float m_new = fmaxf(m_i[r], mx);  // finite: every group holds >= 1 valid token
-      const float alpha = fast_exp2(m_i[r] - m_new);
+      m_new[r] = fmaxf(m_i[r], mx);  // finite: every group holds >= 1 valid token
+      need = need || (m_new[r] - m_i[r] > 8.f);
+    }
+    if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float alpha = fast_exp2(m_i[r] - m_new[r]);
+        l_i[r] *= alpha;
+        m_i[r] = m_new[r];
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+          acc[j][2 * r] *= alpha;
+          acc[j][2 * r + 1] *= alpha;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
       float rs = 0.f;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        s[j][2 * r] = fast_exp2(s[j][2 * r] - m_new);
-        s[j][2 * r + 1] = fast_exp2(s[j][2 * r + 1] - m_new);
+        s[j][2 * r] = fast_exp2(s[j][2 * r] - m_i[r]);
+        s[j][2 * r + 1] = fast_exp2(s[j][2 * r + 1] - m_i[r]);
         rs += s[j][2 * r] + s[j][2 * r + 1];
       }
-      l_i[r] = l_i[r] * alpha + rs;
-      m_i[r] = m_new;
-#pragma unroll
-      for (int j = 0; j < D / 8; ++j) {
-        acc[j][2 * r] *= alpha;
-        acc[j][2 * r + 1] *= alpha;
-      }
+      l_i[r] += rs;
     }
     uint32_t pa[4];
     pa[0] = Elem<T>::pack(s[0][0], s[0][1]);

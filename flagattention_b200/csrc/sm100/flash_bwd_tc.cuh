@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(DqTcCfg<D>::kThreads, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(DQ_SDP_FULL + s), 1);
-      mbar_init(bar(DQ_DS_READY + s), 256);
+      mbar_init(bar(DQ_DS_READY + s), 8);
     }
     mbar_init(bar(DQ_DONE), 1);
     fence_barrier_init();
@@ -229,7 +229,8 @@ __global__ void __launch_bounds__(DqTcCfg<D>::kThreads, 1)
       tmem_st16(tlane + C::kColDP + buf * 64 + half * 32, pk);  // inside this thread's own columns
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(DQ_DS_READY + buf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_DS_READY + buf));  // one arrival per warp
     }
 
     if (ok && T_tiles > 0) {
@@ -335,12 +336,12 @@ __global__ void __launch_bounds__(DkdvTcCfg<D>::kThreads, 1)
     *abort_flag = 0;
     mbar_init(bar(KV_KV_FULL), 1);
     for (int s = 0; s < NS; ++s) {
-      mbar_init(bar(KV_QDO_FULL + s), 33);  // the TMA transaction + 32 lanes storing lse / delta
+      mbar_init(bar(KV_QDO_FULL + s), 2);  // the TMA transaction + the warp that stored lse / delta
       mbar_init(bar(KV_QDO_FREE + s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(KV_SDP_FULL + s), 1);
-      mbar_init(bar(KV_PDS_READY + s), 256);
+      mbar_init(bar(KV_PDS_READY + s), 8);
     }
     mbar_init(bar(KV_DONE), 1);
     fence_barrier_init();
@@ -395,7 +396,8 @@ __global__ void __launch_bounds__(DkdvTcCfg<D>::kThreads, 1)
           lse_s[lane + i * 32] = qm < p.M ? p.lse[lbase + qm] * kLog2e : INFINITY;
           dlt_s[lane + i * 32] = qm < p.M ? p.delta[lbase + qm] : 0.f;
         }
-        mbar_arrive(bar(KV_QDO_FULL + st));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(KV_QDO_FULL + st));  // after every lane stored its lse / delta
         ++issued;
       }
       if (!ok && lane == 0) {
@@ -513,7 +515,8 @@ __global__ void __launch_bounds__(DkdvTcCfg<D>::kThreads, 1)
       tmem_st16(tlane + C::kColDP + buf * 64 + half * 32, ds);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(KV_PDS_READY + buf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KV_PDS_READY + buf));  // one arrival per warp
     }
 
     if (ok && T_tiles > 0) {

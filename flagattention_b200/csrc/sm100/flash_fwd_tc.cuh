@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
       mbar_init(bar(V_FULL + s), 1);
       mbar_init(bar(V_FREE + s), 1);
       mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(P_READY + s), 128);
+      mbar_init(bar(P_READY + s), 4);
       mbar_init(bar(PV_DONE + s), 1);
     }
     fence_barrier_init();
@@ -215,9 +215,16 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
         for (int c = 0; c < BN; ++c)
           if (c >= limit) s[c] = -INFINITY;
       }
-      float mx = s[0];
+      // four independent chains instead of one 64-deep dependency chain
+      float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int c = 1; c < BN; ++c) mx = fmaxf(mx, s[c]);
+      for (int c = 4; c < BN; c += 4) {
+        mx4[0] = fmaxf(mx4[0], s[c]);
+        mx4[1] = fmaxf(mx4[1], s[c + 1]);
+        mx4[2] = fmaxf(mx4[2], s[c + 2]);
+        mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx);
       if (j == 0) {
         m_used = m_new;
@@ -250,19 +257,20 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_ms = -m_eff * qk_scale;
       uint32_t pk[BN / 2];
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < BN; c += 2) {
         const float p0 = ex2(fmaf(s[c], qk_scale, neg_ms));
         const float p1 = ex2(fmaf(s[c + 1], qk_scale, neg_ms));
-        rs += p0 + p1;
+        rs4[(c >> 1) & 3] += p0 + p1;
         pk[c >> 1] = TcElem<T>::pack(p0, p1);
       }
-      l += rs;
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       tmem_st32(scol, reinterpret_cast<const uint32_t(&)[32]>(pk));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(P_READY + st));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_READY + st));  // one arrival per warp
     }
 
     // epilogue: O / l -> global, log-normaliser

@@ -40,7 +40,7 @@ static int launch_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tens
   BwdTcParams p = make_params(s, lse, delta);
   p.dq = dq->ptr, p.sdq = strides_of(dq);
   dim3 grid((s->M + C::BM - 1) / C::BM, s->B * s->H, 1);
-  kern<<<grid, C::kThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
+  kern<<<grid, kBwdThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
   FA_CHECK_LAUNCH();
   return FA_OK;
 }
@@ -63,7 +63,7 @@ static int launch_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, const fa_te
   BwdTcParams p = make_params(s, lse, delta);
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
   dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
-  kern<<<grid, C::kThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
+  kern<<<grid, kBwdThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
   FA_CHECK_LAUNCH();
   return FA_OK;
 }

@@ -34,6 +34,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FLASH_CFG = dict(B=4, H=32, Hk=32, L=4096, D=128, causal=True, dtype="bf16")
+PIECEWISE_CFG = dict(B=1, H=48, L=16384, D=128, w=4096, causal=True, dtype="bf16")
 PAGED_CFG = dict(num_seqs=64, q_heads=32, kv_heads=8, head=128, block=16, ctx_lo=1024, ctx_hi=32768,
                  partition=512, num_splits=64)
 
@@ -250,6 +251,44 @@ def run_flash(args, dist, rank, world, device):
                 launches=4 * args.steps)
 
 
+def run_piecewise(args, dist, rank, world, device):
+    """piecewise_attention fwd+bwd at the Aquila-2-34B-shaped configuration (device-resident)."""
+    import flagattention_b200 as fa
+    c = PIECEWISE_CFG
+    B, H, L, D, w = c["B"], c["H"], c["L"], c["D"], c["w"]
+    gen = torch.Generator(device=device).manual_seed(10086 + 4 + rank)
+    mk = lambda: torch.randn((B, H, L, D), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    q1, k1, q2, k2, v, do = (mk() for _ in range(6))
+    ins = [t.requires_grad_() for t in (q1, k1, q2, k2, v)]
+
+    def step():
+        o = fa.piecewise_attention(*ins, w, causal=True)
+        torch.autograd.grad(o, ins, do)
+
+    for _ in range(3):
+        step()
+    steps = max(3, min(args.steps, 5))
+    barrier(dist)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize()
+    barrier(dist)
+    ms = max_over_ranks(dist, t0.elapsed_time(t1), device) / steps
+    fwd, bwd = flash_flops(B, H, L, L, D, True)      # one score product per pair: the minimal algorithm
+    ref_fwd = 1.5 * fwd                                 # the reference benchmark counts 3 forward matmuls
+    ref_bwd = ref_fwd * 8.0 / 3.0
+    return dict(metric="piecewise_attention fwd+bwd TFLOP/s", value=round(world * (fwd + bwd) / (ms * 1e-3) / 1e12, 2),
+                unit="TFLOP/s", ms_per_step=round(ms, 3), steps=steps,
+                value_reference_convention=round(world * (ref_fwd + ref_bwd) / (ms * 1e-3) / 1e12, 2),
+                config=dict(workload="piecewise_attention fwd+bwd bf16, device-resident", **c,
+                            flops_convention="primary: flash-equivalent (each pair needs one of the two "
+                                             "score products); secondary: the reference benchmark's 3 "
+                                             "forward matmuls, backward x 8/3"))
+
+
 def make_paged_inputs(device, seed):
     c = PAGED_CFG
     gen = torch.Generator().manual_seed(seed)
@@ -394,7 +433,8 @@ def main():
     ap.add_argument("--skip-paged", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling)")
-    ap.add_argument("--only", default=None, choices=["flash", "paged"],
+    ap.add_argument("--skip-piecewise", action="store_true")
+    ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise"],
                     help="run one workload only (profiling); the JSON line is then partial")
     ap.add_argument("--paged-seqs", type=int, default=PAGED_CFG["num_seqs"],
                     help="number of sequences of the paged workload (smaller for profiler captures)")
@@ -417,8 +457,14 @@ def main():
         if rank == 0:
             print(json.dumps({"partial": True, "paged": paged}), flush=True)
         return
+    if args.only == "piecewise":
+        pw = run_piecewise(args, dist, rank, world, device)
+        if rank == 0:
+            print(json.dumps({"partial": True, "piecewise": pw}), flush=True)
+        return
     fl = run_flash(args, dist, rank, world, device)
     paged = None if (args.skip_paged or args.only == "flash") else run_paged(args, dist, rank, world, device)
+    pw = None if (args.skip_piecewise or args.only == "flash") else run_piecewise(args, dist, rank, world, device)
     cpu = None
     if rank == 0 and not args.skip_cpu and world == 1:
         cpu, _ = cpu_flash_sample(2)
@@ -436,6 +482,7 @@ def main():
                        "l2": "inputs (4 x 128 MiB) are larger than the 126 MB L2"},
             "roofline": fl["roofline"], "cpu_baseline": cpu, "e2e": fl["e2e"],
             "gpu_launches": fl["launches"], "clocks": fl["clocks"], "paged": paged,
+            "piecewise": pw,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

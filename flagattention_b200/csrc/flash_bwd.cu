@@ -91,6 +91,15 @@ int flash_bwd_dkdv_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_ten
                       const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                       const float *delta, const fa_tensor4 *dk, const fa_tensor4 *dv,
                       cudaStream_t stream);
+int piecewise_bwd_dq_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q1, const fa_tensor4 *k1,
+                        const fa_tensor4 *q2, const fa_tensor4 *k2, const fa_tensor4 *v,
+                        const fa_tensor4 *d_o, const float *lse, const float *delta,
+                        const fa_tensor4 *dq1, const fa_tensor4 *dq2, cudaStream_t stream);
+int piecewise_bwd_dkdv_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q1,
+                          const fa_tensor4 *k1, const fa_tensor4 *q2, const fa_tensor4 *k2,
+                          const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                          const float *delta, const fa_tensor4 *dk1, const fa_tensor4 *dk2,
+                          const fa_tensor4 *dv, cudaStream_t stream);
 }  // namespace tc
 
 }  // namespace fa
@@ -170,6 +179,10 @@ extern "C" int fa_piecewise_bwd_dkdv(const fa_flash_shape *s, int32_t dist_thres
   if (s->H != s->Hk) return FA_ERR_BAD_ARG;
   if (int st = validate_tensors({q1, k1, q2, k2, v, d_o, dk1, dk2, dv})) return st;
   if (!lse || !delta) return FA_ERR_BAD_ARG;
+  const int tc_status =
+      tc::piecewise_bwd_dkdv_tc(s, dist_threshold, q1, k1, q2, k2, v, d_o, lse, delta, dk1, dk2, dv,
+                                static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   BwdParams p = make_bwd(s, q1, k1, v, d_o, lse, delta);
   p.q2 = q2->ptr, p.k2 = k2->ptr, p.sq2 = strides_of(q2), p.sk2 = strides_of(k2);
   p.w = dist_threshold;
@@ -187,6 +200,10 @@ extern "C" int fa_piecewise_bwd_dq(const fa_flash_shape *s, int32_t dist_thresho
   if (s->H != s->Hk) return FA_ERR_BAD_ARG;
   if (int st = validate_tensors({q1, k1, q2, k2, v, d_o, dq1, dq2})) return st;
   if (!lse || !delta) return FA_ERR_BAD_ARG;
+  const int tc_status =
+      tc::piecewise_bwd_dq_tc(s, dist_threshold, q1, k1, q2, k2, v, d_o, lse, delta, dq1, dq2,
+                              static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   BwdParams p = make_bwd(s, q1, k1, v, d_o, lse, delta);
   p.q2 = q2->ptr, p.k2 = k2->ptr, p.sq2 = strides_of(q2), p.sk2 = strides_of(k2);
   p.w = dist_threshold;

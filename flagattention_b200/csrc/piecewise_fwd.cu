@@ -21,6 +21,12 @@ struct PwFwdLaunch {
   }
 };
 
+namespace tc {
+int piecewise_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q1, const fa_tensor4 *k1,
+                     const fa_tensor4 *q2, const fa_tensor4 *k2, const fa_tensor4 *v,
+                     const fa_tensor4 *o, float *lse, cudaStream_t stream);
+}
+
 }  // namespace fa
 
 using namespace fa;
@@ -33,6 +39,10 @@ extern "C" int fa_piecewise_fwd(const fa_flash_shape *s, int32_t dist_threshold,
   if (s->H != s->Hk) return FA_ERR_BAD_ARG;
   if (int st = validate_tensors({q1, k1, q2, k2, v, o})) return st;
   if (!lse) return FA_ERR_BAD_ARG;
+  // head_dim 64 / 128 run on tcgen05; everything else on the shape-generic kernel
+  const int tc_status = tc::piecewise_fwd_tc(s, dist_threshold, q1, k1, q2, k2, v, o, lse,
+                                             static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   FwdParams p{};
   p.q = q1->ptr, p.k = k1->ptr, p.q2 = q2->ptr, p.k2 = k2->ptr, p.v = v->ptr;
   p.sq = strides_of(q1), p.sk = strides_of(k1), p.sq2 = strides_of(q2), p.sk2 = strides_of(k2);

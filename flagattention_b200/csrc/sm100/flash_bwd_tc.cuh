@@ -31,6 +31,12 @@ struct BwdTcParams {
   int B, H, Hk, M, N;
   int causal;
   float sm_scale;
+  // piecewise_attention runs each kernel twice: mode 1 = near branch (pairs whose distance
+  // (m + N - M) - n is below w, scored with q1.k1), mode 2 = far branch (distance >= w, q2.k2);
+  // every launch only visits tiles that hold a pair of its branch and masks the others out.
+  // mode 0 = flash_attention.
+  int mode, w;
+  int dv_accumulate;  // dK/dV kernel: add dV to what `dv` already holds (second piecewise launch)
   int *status;
 };
 
@@ -98,7 +104,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int num_m_tiles = (p.M + BM - 1) / BM;
   int mt_lo = 0;
   if (p.causal) mt_lo = max(0, n0 - p_seq) / BM;
-  const int tiles = max(0, num_m_tiles - mt_lo);
+  int mt_hi = num_m_tiles;
+  if (p.mode == 1) {  // query tiles that hold a near pair: m0 < w - p_seq + n0 + BN - 1
+    const int lim = p.w - p_seq + n0 + BN - 1;
+    mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+  } else if (p.mode == 2) {  // query tiles that hold a far pair: m0 >= w - p_seq + n0 - (BM - 1)
+    const int lim = p.w - p_seq + n0 - (BM - 1);
+    mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+  }
+  const int tiles = max(0, mt_hi - mt_lo);
   const int T_tiles = tiles * G;
 
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
@@ -274,9 +288,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const int64_t li = ((int64_t)b * p.H + h) * p.M + qm_lane;
       const float lse_lane = qm_lane < p.M ? p.lse[li] * kLog2e : INFINITY;
       const float dlt_lane = qm_lane < p.M ? p.delta[li] : 0.f;
-      // first visible query column of this key row inside this thread's 32 columns
-      int cmin = 0;
+      // visible query columns of this key row inside this thread's 32 columns: [cmin, cmax)
+      int cmin = 0, cmax = 32;
       if (p.causal) cmin = key - p_seq - m0 - cg * 32;
+      if (p.mode) {
+        const int cnear = p.w + key - p_seq - m0 - cg * 32;  // columns below it are near pairs
+        if (p.mode == 1) cmax = min(cmax, cnear);
+        else cmin = max(cmin, cnear);
+      }
       if (!key_ok) cmin = 32;
 
       // ---- phase 1: P^T = exp2(S^T * scale - lse), written over S^T ----
@@ -295,8 +314,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const float l1 = __shfl_sync(0xffffffffu, lse_lane, c + 1);
         float p0 = ex2(fmaf(__uint_as_float(sr[c]), qk_scale, -l0));
         float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), qk_scale, -l1));
-        if (c < cmin) p0 = 0.f;
-        if (c + 1 < cmin) p1 = 0.f;
+        if (c < cmin || c >= cmax) p0 = 0.f;
+        if (c + 1 < cmin || c + 1 >= cmax) p1 = 0.f;
         pv[c] = p0, pv[c + 1] = p1;
         pk[c >> 1] = TcElem<T>::pack(p0, p1);
       }
@@ -350,6 +369,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (which == 1 && p.dv_accumulate && key_ok) {
+          // second piecewise launch: add the first launch's dV
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 old = *reinterpret_cast<const uint4 *>(orow + col0 + i * 8);
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const float2 f = TcElem<T>::unpack(ow[e2]);
+              ov[8 * i + 2 * e2] = __float_as_uint(__uint_as_float(ov[8 * i + 2 * e2]) + f.x);
+              ov[8 * i + 2 * e2 + 1] = __float_as_uint(__uint_as_float(ov[8 * i + 2 * e2 + 1]) + f.y);
+            }
+          }
         }
         if (key_ok) store_row32<T>(orow + col0, ov, scale);
       }
@@ -411,7 +444,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int p_seq = p.N - p.M;
   int n_hi = p.N;
   if (p.causal) n_hi = min(n_hi, p_seq + m0 + BM);
-  const int T_tiles = n_hi > 0 ? (n_hi + BN - 1) / BN : 0;
+  const int T_all = n_hi > 0 ? (n_hi + BN - 1) / BN : 0;
+  // piecewise: key tiles [0, jf) are entirely far, [jn, T) entirely near
+  int t_lo = 0, t_hi = T_all, jf = 0, jn = 0;
+  if (p.mode) {
+    const int x = m0 + p_seq - (BN - 1) - p.w, y = m0 + BM - 1 + p_seq - p.w;
+    jf = x < 0 ? 0 : min(T_all, x / BN + 1);
+    jn = y < 0 ? 0 : min(T_all, y / BN + 1);
+    if (p.mode == 1) t_lo = jf; else t_hi = jn;
+  }
+  const int T_tiles = max(0, t_hi - t_lo);
 
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
 
@@ -459,7 +501,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       int issued_k = 0, issued_v = 0;
       bool ok = true;
       for (int t = 0; t < T_tiles; ++t) {
-        const int sk = t % NK, sv = t % NV, n0 = t * BN;
+        const int sk = t % NK, sv = t % NV, n0 = (t_lo + t) * BN;
         ok = mbar_wait(bar(DQ_K_FREE + sk), ((t / NK) & 1) ^ 1, actx, 401);
         if (!ok) break;
         mbar_expect_tx(bar(DQ_K_FULL + sk), C::kTile);
@@ -566,7 +608,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     bool ok = true;
 
     for (int t = 0; t < T_tiles; ++t) {
-      const int buf = t & 1, n0 = t * BN;
+      const int buf = t & 1, j = t_lo + t, n0 = j * BN;
       // ---- phase 1: P = exp2(S * scale - lse), kept in registers ----
       ok = mbar_wait(bar(DQ_S_FULL), t & 1, actx, 601);
       ok = __all_sync(0xffffffffu, ok);
@@ -578,18 +620,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_S_CONSUMED));
+      // valid key columns of this row inside this thread's 32 columns: [lo, hi)
       const bool need_mask = (n0 + BN > p.N) || (p.causal && (n0 + BN - 1 > m0 + p_seq));
-      int limit = 32;
+      int lo = 0, hi = 32;
       if (need_mask) {
-        limit = p.N - n0;
-        if (p.causal) limit = min(limit, row + p_seq - n0 + 1);
-        limit -= cg * 32;
+        hi = p.N - n0;
+        if (p.causal) hi = min(hi, row + p_seq - n0 + 1);
+        hi -= cg * 32;
+      }
+      if (p.mode) {
+        const int cfar = row + p_seq - p.w - n0 - cg * 32;  // columns <= cfar are far pairs
+        if (p.mode == 2) hi = min(hi, cfar + 1);
+        else lo = max(lo, cfar + 1);
       }
       float pv[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         const float pe = ex2(fmaf(__uint_as_float(sr[c]), qk_scale, -lse2));
-        pv[c] = c < limit ? pe : 0.f;
+        pv[c] = (c >= lo && c < hi) ? pe : 0.f;
       }
       // ---- phase 2: dS = P * (dP - delta), written over dP ----
       ok = mbar_wait(bar(DQ_DP_FULL + buf), (t >> 1) & 1, actx, 602);

@@ -15,39 +15,57 @@ bool generic_forced() {
   return e && e[0] == '1';
 }
 
-template <typename T, int D>
-static int launch_fwd_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
-                         const fa_tensor4 *v, const fa_tensor4 *o, float *lse,
-                         cudaStream_t stream) {
+template <typename T, int D, bool PW>
+static int launch_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q, const fa_tensor4 *k,
+                         const fa_tensor4 *q2, const fa_tensor4 *k2, const fa_tensor4 *v,
+                         const fa_tensor4 *o, float *lse, cudaStream_t stream) {
   using C = FwdTcCfg<D>;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mq2, mk2;
   if (!make_map_bhld(&mq, q, s->dtype, s->B, s->H, s->M, D, C::BM) ||
       !make_map_bhld(&mk, k, s->dtype, s->B, s->Hk, s->N, D, C::BN) ||
-      !make_map_bhld(&mv, v, s->dtype, s->B, s->Hk, s->N, D, C::BN))
+      !make_map_bhld(&mv, v, s->dtype, s->B, s->Hk, s->N, D, C::BN) ||
+      !make_map_bhld(&mq2, q2, s->dtype, s->B, s->H, s->M, D, C::BM) ||
+      !make_map_bhld(&mk2, k2, s->dtype, s->B, s->Hk, s->N, D, C::BN))
     return 1;  // layout not expressible as a tensor map: caller falls back to the generic kernel
-  auto kern = flash_fwd_tc_kernel<T, D>;
+  auto kern = flash_fwd_tc_kernel<T, D, PW>;
   static unsigned long long done = 0;
   if (int st = ensure_dyn_smem(kern, C::kTotal, &done)) return st;
   FwdTcParams p{};
   p.o = o->ptr, p.lse = lse, p.so = strides_of(o);
   p.B = s->B, p.H = s->H, p.Hk = s->Hk, p.M = s->M, p.N = s->N;
-  p.causal = s->causal, p.sm_scale = s->sm_scale;
+  p.causal = s->causal, p.sm_scale = s->sm_scale, p.w = w;
   p.status = device_status_word();
   dim3 grid((s->M + C::BM - 1) / C::BM, s->B * s->H, 1);
-  kern<<<grid, C::kThreads, C::kTotal, stream>>>(mq, mk, mv, p);
+  kern<<<grid, C::kThreads, C::kTotal, stream>>>(mq, mk, mv, mq2, mk2, p);
   FA_CHECK_LAUNCH();
   return FA_OK;
 }
 
-// Returns FA_OK / a negative status, or 1 when this path does not cover the call.
+static bool covered(const fa_flash_shape *s) {
+  return !generic_forced() && s->sm_scale > 0.f && (s->D == 64 || s->D == 128);
+}
+
+// Return FA_OK / a negative status, or 1 when this path does not cover the call.
 int flash_fwd_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
                  const fa_tensor4 *v, const fa_tensor4 *o, float *lse, cudaStream_t stream) {
-  if (generic_forced() || !(s->sm_scale > 0.f) || (s->D != 64 && s->D != 128)) return 1;
+  if (!covered(s)) return 1;
   if (s->dtype == FA_F16)
-    return s->D == 128 ? launch_fwd_tc<__half, 128>(s, q, k, v, o, lse, stream)
-                       : launch_fwd_tc<__half, 64>(s, q, k, v, o, lse, stream);
-  return s->D == 128 ? launch_fwd_tc<__nv_bfloat16, 128>(s, q, k, v, o, lse, stream)
-                     : launch_fwd_tc<__nv_bfloat16, 64>(s, q, k, v, o, lse, stream);
+    return s->D == 128 ? launch_fwd_tc<__half, 128, false>(s, 0, q, k, q, k, v, o, lse, stream)
+                       : launch_fwd_tc<__half, 64, false>(s, 0, q, k, q, k, v, o, lse, stream);
+  return s->D == 128 ? launch_fwd_tc<__nv_bfloat16, 128, false>(s, 0, q, k, q, k, v, o, lse, stream)
+                     : launch_fwd_tc<__nv_bfloat16, 64, false>(s, 0, q, k, q, k, v, o, lse, stream);
+}
+
+int piecewise_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q1, const fa_tensor4 *k1,
+                     const fa_tensor4 *q2, const fa_tensor4 *k2, const fa_tensor4 *v,
+                     const fa_tensor4 *o, float *lse, cudaStream_t stream) {
+  if (!covered(s) || w > (1 << 29) || w < -(1 << 29)) return 1;
+  if (s->dtype == FA_F16)
+    return s->D == 128 ? launch_fwd_tc<__half, 128, true>(s, w, q1, k1, q2, k2, v, o, lse, stream)
+                       : launch_fwd_tc<__half, 64, true>(s, w, q1, k1, q2, k2, v, o, lse, stream);
+  return s->D == 128
+             ? launch_fwd_tc<__nv_bfloat16, 128, true>(s, w, q1, k1, q2, k2, v, o, lse, stream)
+             : launch_fwd_tc<__nv_bfloat16, 64, true>(s, w, q1, k1, q2, k2, v, o, lse, stream);
 }
 
 }  // namespace tc

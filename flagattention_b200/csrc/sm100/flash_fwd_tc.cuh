@@ -27,6 +27,7 @@ struct FwdTcParams {
   int B, H, Hk, M, N;
   int causal;
   float sm_scale;
+  int w;  // piecewise distance threshold (PW kernels only)
   int *status;
 };
 
@@ -48,13 +49,21 @@ struct FwdTcCfg {
 };
 
 enum FwdBar { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, P_READY = 11,
-              PV_DONE = 13 };
+              PV_DONE = 13, Q_FREE = 15 };
 
-template <typename T, int D>
+// PW = piecewise_attention: the score of (m, n) is q2.k2 when (m + N - M) - n >= w, else q.k.
+// The key tiles of a CTA are then walked as a list of (tile, branch) entries: first every tile
+// that holds a far pair with (q2, k2), then every tile that holds a near pair with (q, k).  A
+// tile that straddles the threshold appears twice, each time masked to its own branch, so each
+// entry is an ordinary flash tile and the online softmax simply sees a few more tiles.  Q is
+// re-loaded once, at the switch from the far to the near entries.
+template <typename T, int D, bool PW>
 __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
     flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                         const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, const FwdTcParams p) {
+                        const __grid_constant__ CUtensorMap map_v,
+                        const __grid_constant__ CUtensorMap map_q2,
+                        const __grid_constant__ CUtensorMap map_k2, const FwdTcParams p) {
   using C = FwdTcCfg<D>;
   constexpr int BM = C::BM, BN = C::BN, KSUB = C::KSUB;
   extern __shared__ uint8_t smem_unaligned[];
@@ -74,6 +83,16 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
   int n_hi = p.N;
   if (p.causal) n_hi = min(n_hi, p_seq + m0 + BM);
   const int T_tiles = n_hi > 0 ? (n_hi + BN - 1) / BN : 0;
+  // piecewise schedule: tiles [0, jf) are entirely far, [jn, T) entirely near, [jf, jn) straddle
+  int jf = 0, jn = 0;
+  if (PW) {
+    const int x = m0 + p_seq - (BN - 1) - p.w, y = m0 + BM - 1 + p_seq - p.w;
+    jf = x < 0 ? 0 : min(T_tiles, x / BN + 1);
+    jn = y < 0 ? 0 : min(T_tiles, y / BN + 1);
+  }
+  const int E2 = jn;                    // entries of the far branch: tiles 0 .. jn-1
+  const int E = E2 + (T_tiles - jf);    // then the near branch: tiles jf .. T-1
+  const bool reload_q = PW && E2 > 0 && E2 < E;
 
   // a wait that ran out earlier (this launch or a previous one) poisons the device status word:
   // do no work until the host has read and cleared it
@@ -82,6 +101,7 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar(Q_FULL), 1);
+    mbar_init(bar(Q_FREE), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(K_FULL + s), 1);
       mbar_init(bar(K_FREE + s), 1);
@@ -104,23 +124,34 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0 && T_tiles > 0) {
+    if (lane == 0 && E > 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
+      const CUtensorMap *first_q = (PW && E2 > 0) ? &map_q2 : &map_q;
       mbar_expect_tx(bar(Q_FULL), C::kQBytes);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kQ + s * BM * 128, &map_q, bar(Q_FULL), s * 64, m0, h, b);
+        tma_load_4d(smem + C::kQ + s * BM * 128, first_q, bar(Q_FULL), s * 64, m0, h, b);
       int issued_k = 0, issued_v = 0;
       bool ok = true;
-      for (int j = 0; j < T_tiles && ok; ++j) {
-        const int st = j & 1, ph = (j >> 1) & 1, n0 = j * BN;
+      for (int e = 0; e < E && ok; ++e) {
+        const bool far = PW && e < E2;
+        const int j = (PW && e >= E2) ? jf + (e - E2) : e;
+        const int st = e & 1, ph = (e >> 1) & 1, n0 = j * BN;
+        if (reload_q && e == E2) {
+          // every S of the far branch has been computed: swap q2 for q
+          ok = mbar_wait(bar(Q_FREE), 0, actx, 103);
+          if (!ok) break;
+          mbar_expect_tx(bar(Q_FULL), C::kQBytes);
+          for (int s = 0; s < KSUB; ++s)
+            tma_load_4d(smem + C::kQ + s * BM * 128, &map_q, bar(Q_FULL), s * 64, m0, h, b);
+        }
         ok = mbar_wait(bar(K_FREE + st), ph ^ 1, actx, 101);
         if (!ok) break;
         mbar_expect_tx(bar(K_FULL + st), C::kKVBytes);
         for (int s = 0; s < KSUB; ++s)
-          tma_load_4d(smem + C::kK + st * C::kKVBytes + s * BN * 128, &map_k, bar(K_FULL + st),
-                      s * 64, n0, hk, b);
+          tma_load_4d(smem + C::kK + st * C::kKVBytes + s * BN * 128, far ? &map_k2 : &map_k,
+                      bar(K_FULL + st), s * 64, n0, hk, b);
         ++issued_k;
         ok = mbar_wait(bar(V_FREE + st), ph ^ 1, actx, 102);
         if (!ok) break;
@@ -141,46 +172,51 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0 && T_tiles > 0) {
+    if (lane == 0 && E > 0) {
       constexpr uint32_t idesc_s = instr_desc_f16(BM, BN, TcElem<T>::kFormat, 0, 0);
       constexpr uint32_t idesc_pv = instr_desc_f16(BM, D, TcElem<T>::kFormat, 0, 1);
+      // descriptor low words: the issuing thread only adds a constant per MMA
+      const uint32_t q_lo = smem_desc_lo(smem + C::kQ, 0);
+      const uint32_t k_lo = smem_desc_lo(smem + C::kK, 0);
+      const uint32_t v_lo = smem_desc_lo(smem + C::kV, BN * 128);
+      constexpr uint32_t kKV16 = C::kKVBytes >> 4;
       bool ok = mbar_wait(bar(Q_FULL), 0, actx, 201);
       auto issue_pv = [&](int i) -> bool {
         const int st = i & 1, ph = (i >> 1) & 1;
         if (!mbar_wait(bar(V_FULL + st), ph, actx, 203)) return false;
         if (!mbar_wait(bar(P_READY + st), ph, actx, 204)) return false;
         tc_fence_after();
-        const uint32_t vbase = smem + C::kV + st * C::kKVBytes;
+        const uint32_t b_lo = v_lo + st * kKV16;
+        const uint32_t a_col = tmem + (st ? C::kColS1 : C::kColS0);
+        const uint32_t acc = i > 0 ? 1u : 0u;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t bd = smem_desc_sw128(vbase + kk * 16 * 128, BN * 128, 1024);
-          mma_ts(tmem + C::kColO, tmem + (st ? C::kColS1 : C::kColS0) + kk * 8, bd, idesc_pv,
-                 (i > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_ts_lo(tmem + C::kColO, a_col + kk * 8, b_lo + ((kk * 16 * 128) >> 4), idesc_pv,
+                    kk > 0 ? 1u : acc);
         mma_commit(bar(PV_DONE + st));
         mma_commit(bar(V_FREE + st));
         return true;
       };
-      for (int j = 0; j < T_tiles && ok; ++j) {
-        const int st = j & 1, ph = (j >> 1) & 1;
-        ok = mbar_wait(bar(K_FULL + st), ph, actx, 202);
+      for (int e = 0; e < E && ok; ++e) {
+        const int st = e & 1, ph = (e >> 1) & 1;
+        if (reload_q && e == E2) ok = mbar_wait(bar(Q_FULL), 1, actx, 206);
+        if (ok) ok = mbar_wait(bar(K_FULL + st), ph, actx, 202);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t kbase = smem + C::kK + st * C::kKVBytes;
+        const uint32_t b_lo = k_lo + st * kKV16;
+        const uint32_t d_col = tmem + (st ? C::kColS1 : C::kColS0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t ad =
-              smem_desc_sw128(smem + C::kQ + (k / 4) * BM * 128 + (k % 4) * 32, 0, 1024);
-          const uint64_t bd = smem_desc_sw128(kbase + (k / 4) * BN * 128 + (k % 4) * 32, 0, 1024);
-          mma_ss(tmem + (st ? C::kColS1 : C::kColS0), ad, bd, idesc_s, k > 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          mma_ss_lo(d_col, q_lo + (((k / 4) * BM * 128 + (k % 4) * 32) >> 4),
+                    b_lo + (((k / 4) * BN * 128 + (k % 4) * 32) >> 4), idesc_s, k > 0 ? 1u : 0u);
         mma_commit(bar(S_FULL + st));
         mma_commit(bar(K_FREE + st));
-        if (j >= 1) ok = issue_pv(j - 1);
+        if (reload_q && e == E2 - 1) mma_commit(bar(Q_FREE));
+        if (e >= 1) ok = issue_pv(e - 1);
       }
-      if (ok) ok = issue_pv(T_tiles - 1);
+      if (ok) ok = issue_pv(E - 1);
       // the last commit's arrive must land before this CTA's shared memory is given back
-      if (ok) mbar_wait(bar(V_FREE + ((T_tiles - 1) & 1)), ((T_tiles - 1) >> 1) & 1, actx, 205);
+      if (ok) mbar_wait(bar(V_FREE + ((E - 1) & 1)), ((E - 1) >> 1) & 1, actx, 205);
     }
   } else {
     // ------------------------------ softmax warps -----------------------------
@@ -192,8 +228,10 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < T_tiles; ++j) {
-      const int st = j & 1, ph = (j >> 1) & 1, n0 = j * BN;
+    for (int e = 0; e < E; ++e) {
+      const bool far = PW && e < E2;
+      const int j = (PW && e >= E2) ? jf + (e - E2) : e;
+      const int st = e & 1, ph = (e >> 1) & 1, n0 = j * BN;
       ok = mbar_wait(bar(S_FULL + st), ph, actx, 301);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -207,13 +245,22 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
 #pragma unroll
       for (int c = 0; c < BN; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
 
-      const bool need_mask = (n0 + BN > p.N) || (p.causal && (n0 + BN - 1 > m0 + p_seq));
+      // valid columns of this row are [lo, hi)
+      bool need_mask = (n0 + BN > p.N) || (p.causal && (n0 + BN - 1 > m0 + p_seq));
+      int lo = 0, hi = BN;
       if (need_mask) {
-        int limit = p.N - n0;
-        if (p.causal) limit = min(limit, row + p_seq - n0 + 1);
+        hi = p.N - n0;
+        if (p.causal) hi = min(hi, row + p_seq - n0 + 1);
+      }
+      if (PW) {
+        const int cfar = row + p_seq - p.w - n0;  // columns <= cfar are far pairs of this row
+        if (far && j >= jf) hi = min(hi, cfar + 1), need_mask = true;
+        if (!far && j < jn) lo = max(lo, cfar + 1), need_mask = true;
+      }
+      if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BN; ++c)
-          if (c >= limit) s[c] = -INFINITY;
+          if (c < lo || c >= hi) s[c] = -INFINITY;
       }
       // four independent chains instead of one 64-deep dependency chain
       float mx4[4] = {s[0], s[1], s[2], s[3]};
@@ -226,12 +273,12 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx);
-      if (j == 0) {
+      if (e == 0) {
         m_used = m_new;
       } else {
         const bool need = (m_new - m_used) * qk_scale > 8.f;
         if (__any_sync(0xffffffffu, need)) {
-          const int pj = j - 1;
+          const int pj = e - 1;
           ok = mbar_wait(bar(PV_DONE + (pj & 1)), (pj >> 1) & 1, actx, 302);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -274,8 +321,8 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
     }
 
     // epilogue: O / l -> global, log-normaliser
-    if (ok && T_tiles > 0) {
-      const int lj = T_tiles - 1;
+    if (ok && E > 0) {
+      const int lj = E - 1;
       ok = mbar_wait(bar(PV_DONE + (lj & 1)), (lj >> 1) & 1, actx, 303);
       ok = __all_sync(0xffffffffu, ok);
     }
@@ -286,7 +333,7 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t ov[32];
-        if (T_tiles > 0) {
+        if (E > 0) {
           tmem_ld32(tlane + C::kColO + c * 32, ov);
           tmem_wait_ld();
         } else {

@@ -246,6 +246,9 @@ struct TcElem;
 template <>
 struct TcElem<__half> {
   static constexpr int kFormat = 0;
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&u));
+  }
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
@@ -254,6 +257,9 @@ struct TcElem<__half> {
 template <>
 struct TcElem<__nv_bfloat16> {
   static constexpr int kFormat = 1;
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
+  }
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);

@@ -83,3 +83,26 @@ def test_golden_fixtures_on_gpu():
         assert_within_2x(o.cpu(), c["ref"]["o"], c["torch"]["o"], "o")
         for h, r, t in zip(grads, c["ref"]["grads"], c["torch"]["grads"]):
             assert_within_2x(h.cpu(), r, t, "grad")
+
+
+@pytest.mark.parametrize("B,H,M,N,D", [(2, 4, 512, 612, 128), (2, 4, 1024, 1034, 64), (1, 3, 700, 700, 128),
+                                       (1, 2, 1500, 1300, 64)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_generic_kernels_at_tensor_core_head_dims(B, H, M, N, D, causal, monkeypatch):
+    """head_dim 64/128 normally run on the tcgen05 kernels; FLAGATTN_B200_GENERIC=1 routes them to the
+    shape-generic kernels, which must meet the same bar."""
+    dtype = torch.bfloat16 if causal else torch.float16
+    q1, k1, q2, k2, v, do = _inputs(B, H, M, N, D, dtype, "BHTD", 1.0, seed=M + D)
+    w = (M // 2) if M < N else (M - N // 2)
+    ins = [t.requires_grad_() for t in (q1, k1, q2, k2, v)]
+    o_ref = oracle.piecewise_attention(*ins, w, causal, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, ins, do)
+    o_tor = oracle.piecewise_attention(*ins, w, causal, upcast=False)
+    g_tor = torch.autograd.grad(o_tor, ins, do)
+    for mode in ("1", "0"):
+        monkeypatch.setenv("FLAGATTN_B200_GENERIC", mode)
+        o = fa.piecewise_attention(*ins, w, causal=causal)
+        g = torch.autograd.grad(o, ins, do)
+        assert_within_2x(o, o_ref, o_tor, f"o generic={mode}")
+        for name, h, r, t in zip(("dq1", "dk1", "dq2", "dk2", "dv"), g, g_ref, g_tor):
+            assert_within_2x(h, r, t, f"{name} generic={mode}")

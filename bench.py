@@ -226,13 +226,25 @@ def run_flash(args, dist, rank, world, device):
     e2e_steps = max(2, min(args.steps, 5))
     outs_host = [torch.empty((B, H, L, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
 
+    # The step is pipelined over the batch dimension on two streams, so that the host-to-device
+    # copy of one batch element overlaps the kernels and the device-to-host copy of the previous one.
+    streams = [torch.cuda.Stream(device=device) for _ in range(2)]
+
     def e2e_step():
-        qd, kd, vd, dod = (t.to(device, non_blocking=True) for t in host)
-        qd.requires_grad_(), kd.requires_grad_(), vd.requires_grad_()
-        o = fa.flash_attention(qd, kd, vd, causal=True)
-        grads = torch.autograd.grad(o, (qd, kd, vd), dod)
-        for dst, src in zip(outs_host, (o.detach(), *grads)):
-            dst.copy_(src, non_blocking=True)
+        cur = torch.cuda.current_stream(device)
+        for st in streams:
+            st.wait_stream(cur)
+        for bi in range(B):
+            st = streams[bi % 2]
+            with torch.cuda.stream(st):
+                qd, kd, vd, dod = (t[bi:bi + 1].to(device, non_blocking=True) for t in host)
+                qd.requires_grad_(), kd.requires_grad_(), vd.requires_grad_()
+                o = fa.flash_attention(qd, kd, vd, causal=True)
+                grads = torch.autograd.grad(o, (qd, kd, vd), dod)
+                for dst, src in zip(outs_host, (o.detach(), *grads)):
+                    dst[bi:bi + 1].copy_(src, non_blocking=True)
+        for st in streams:
+            cur.wait_stream(st)
 
     e2e_step()
     barrier(dist)

@@ -1,0 +1,79 @@
+"""Multi-rank host logic on CPU: shard helpers, and a world_size-2 gloo run that shards a decode batch,
+computes each shard with the oracle (the stand-in for the per-rank GPU operator) and reassembles it."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from flagattention_b200 import dist as fdist
+
+
+def test_shard_batch_heads_partitions_exactly():
+    for B, Hk, world in [(4, 32, 8), (4, 32, 3), (1, 48, 8), (2, 1, 4), (3, 5, 2)]:
+        seen = []
+        sizes = []
+        for r in range(world):
+            runs = fdist.shard_batch_heads(B, Hk, world, r)
+            n = 0
+            for b, h0, h1 in runs:
+                assert 0 <= b < B and 0 <= h0 < h1 <= Hk
+                seen += [(b, h) for h in range(h0, h1)]
+                n += h1 - h0
+            sizes.append(n)
+        assert sorted(seen) == [(b, h) for b in range(B) for h in range(Hk)]
+        assert max(sizes) - min(sizes) <= 1
+
+
+def test_shard_sequences_lpt_balances():
+    gen = torch.Generator().manual_seed(1)
+    lens = torch.randint(1024, 32769, (64,), generator=gen).tolist()
+    for world in (1, 2, 4, 8):
+        shards = fdist.shard_sequences_lpt(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(64))
+        loads = [sum(lens[i] for i in s) for s in shards]
+        assert max(loads) - min(loads) <= max(lens)          # LPT bound
+        assert max(loads) <= 1.1 * sum(lens) / world
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_dir):
+    import torch.distributed as dist
+    import oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(5)                 # same inputs on every rank
+        S, Hq, Hk, D, BS, NB = 6, 4, 2, 32, 16, 40
+        lens = torch.tensor([100, 17, 64, 1, 90, 33], dtype=torch.int32)
+        q = torch.randn((S, Hq, D), generator=gen).half()
+        kc = torch.randn((NB, Hk, BS, D), generator=gen).half()
+        vc = torch.randn((NB, Hk, BS, D), generator=gen).half()
+        bt = torch.randint(0, NB, (S, 7), generator=gen)
+        shards = fdist.shard_sequences_lpt(lens.tolist(), world)
+        mine = shards[rank]
+        idx = torch.tensor(mine, dtype=torch.long)
+        local = oracle.paged_attention_gathered(q[idx], kc, vc, bt[idx], lens[idx], D ** -0.5)
+        parts = fdist.all_gather_rows(local, [len(s) for s in shards])
+        full = torch.empty_like(q)
+        for s, part in zip(shards, parts):
+            full[torch.tensor(s, dtype=torch.long)] = part
+        want = oracle.paged_attention_gathered(q, kc, vc, bt, lens, D ** -0.5)
+        assert torch.equal(full, want)
+        slowest = fdist.max_over_ranks(1.0 + rank, torch.device("cpu"))
+        assert slowest == float(world)
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_shard_and_gather(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))

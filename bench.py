@@ -72,7 +72,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100", "-f", self.path],
+                 "--format=csv,noheader,nounits", "-lms", "50", "-f", self.path],
                 stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -180,11 +180,19 @@ def run_flash(args, dist, rank, world, device):
         else:
             fl._backward(q, k, v, o, lse, do, True, sm_scale)
 
-    for _ in range(args.warmup):
-        step()
+    # Warm-up: W steps, continued until the GPU has been under this load for half a second, with
+    # the clock sampler already running, so that the clock record covers a loaded GPU even when
+    # the timed region itself is shorter than nvidia-smi's sampling period.
     sampler = ClockSampler(torch.cuda.current_device())
-    barrier(dist)
     sampler.start()
+    t_warm = time.perf_counter()
+    done = 0
+    while done < args.warmup or time.perf_counter() - t_warm < 0.5:
+        step()
+        done += 1
+        if done % 8 == 0:
+            torch.cuda.synchronize()
+    barrier(dist)
     events = []
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()

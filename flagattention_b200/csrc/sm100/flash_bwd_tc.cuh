@@ -288,15 +288,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const int64_t li = ((int64_t)b * p.H + h) * p.M + qm_lane;
       const float lse_lane = qm_lane < p.M ? p.lse[li] * kLog2e : INFINITY;
       const float dlt_lane = qm_lane < p.M ? p.delta[li] : 0.f;
-      // visible query columns of this key row inside this thread's 32 columns: [cmin, cmax)
+      // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
+      // masking at all; the others mask with one unsigned range check per element:
+      // column c is visible iff cmin <= c < cmin + cwidth.
+      bool interior = (n0 + BN <= p.N) && (!p.causal || m0 + p_seq >= n0 + BN - 1);
+      if (p.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
+      if (p.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
       int cmin = 0, cmax = 32;
-      if (p.causal) cmin = key - p_seq - m0 - cg * 32;
+      if (p.causal) cmin = max(cmin, key - p_seq - m0 - cg * 32);
       if (p.mode) {
         const int cnear = p.w + key - p_seq - m0 - cg * 32;  // columns below it are near pairs
         if (p.mode == 1) cmax = min(cmax, cnear);
         else cmin = max(cmin, cnear);
       }
       if (!key_ok) cmin = 32;
+      const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
 
       // ---- phase 1: P^T = exp2(S^T * scale - lse), written over S^T ----
       ok = mbar_wait(bar(KV_S_FULL), t & 1, actx, 901);
@@ -309,15 +315,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       float pv[32];
       uint32_t pk[16];
 #pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float lc = __shfl_sync(0xffffffffu, lse_lane, c);
+        pv[c] = fmaf(__uint_as_float(sr[c]), qk_scale, -lc);
+      }
+      if (!interior) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          pv[c] = ((unsigned)(c - cmin) < cwidth) ? pv[c] : -INFINITY;  // exp2(-inf) = 0
+      }
+#pragma unroll
       for (int c = 0; c < 32; c += 2) {
-        const float l0 = __shfl_sync(0xffffffffu, lse_lane, c);
-        const float l1 = __shfl_sync(0xffffffffu, lse_lane, c + 1);
-        float p0 = ex2(fmaf(__uint_as_float(sr[c]), qk_scale, -l0));
-        float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), qk_scale, -l1));
-        if (c < cmin || c >= cmax) p0 = 0.f;
-        if (c + 1 < cmin || c + 1 >= cmax) p1 = 0.f;
-        pv[c] = p0, pv[c + 1] = p1;
-        pk[c >> 1] = TcElem<T>::pack(p0, p1);
+        pv[c] = ex2(pv[c]);
+        pv[c + 1] = ex2(pv[c + 1]);
+        pk[c >> 1] = TcElem<T>::pack(pv[c], pv[c + 1]);
       }
       tmem_st16(tlane + C::kColS + cg * 32, pk);  // inside this thread's own columns
       tmem_wait_st();
@@ -620,25 +631,31 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_S_CONSUMED));
-      // valid key columns of this row inside this thread's 32 columns: [lo, hi)
-      const bool need_mask = (n0 + BN > p.N) || (p.causal && (n0 + BN - 1 > m0 + p_seq));
-      int lo = 0, hi = 32;
-      if (need_mask) {
-        hi = p.N - n0;
-        if (p.causal) hi = min(hi, row + p_seq - n0 + 1);
-        hi -= cg * 32;
-      }
-      if (p.mode) {
-        const int cfar = row + p_seq - p.w - n0 - cg * 32;  // columns <= cfar are far pairs
-        if (p.mode == 2) hi = min(hi, cfar + 1);
-        else lo = max(lo, cfar + 1);
-      }
+      // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
+      // masking; the others mask with one unsigned range check per element: key column c of this
+      // thread's 32 columns is visible iff lo <= c < lo + width.
+      bool interior = (n0 + BN <= p.N) && (!p.causal || n0 + BN - 1 <= m0 + p_seq);
+      if (p.mode == 1) interior = interior && j >= jn;
+      if (p.mode == 2) interior = interior && j < jf;
       float pv[32];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float pe = ex2(fmaf(__uint_as_float(sr[c]), qk_scale, -lse2));
-        pv[c] = (c >= lo && c < hi) ? pe : 0.f;
+      for (int c = 0; c < 32; ++c) pv[c] = fmaf(__uint_as_float(sr[c]), qk_scale, -lse2);
+      if (!interior) {
+        int lo = 0, hi = p.N - n0;
+        if (p.causal) hi = min(hi, row + p_seq - n0 + 1);
+        hi = min(hi - cg * 32, 32);
+        if (p.mode) {
+          const int cfar = row + p_seq - p.w - n0 - cg * 32;  // columns <= cfar are far pairs
+          if (p.mode == 2) hi = min(hi, cfar + 1);
+          else lo = max(lo, cfar + 1);
+        }
+        const unsigned width = (unsigned)max(hi - lo, 0);
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          pv[c] = ((unsigned)(c - lo) < width) ? pv[c] : -INFINITY;  // exp2(-inf) = 0
       }
+#pragma unroll
+      for (int c = 0; c < 32; ++c) pv[c] = ex2(pv[c]);
       // ---- phase 2: dS = P * (dP - delta), written over dP ----
       ok = mbar_wait(bar(DQ_DP_FULL + buf), (t >> 1) & 1, actx, 602);
       ok = __all_sync(0xffffffffu, ok);

@@ -21,7 +21,7 @@ EXPORTED_SYMBOLS = (
     "fa_num_splits_heuristic", "fa_total_attention", "fa_flash_bwd_delta", "fa_flash_bwd_dkdv",
     "fa_flash_bwd_dq", "fa_piecewise_fwd", "fa_piecewise_bwd_dkdv", "fa_piecewise_bwd_dq",
     "fa_paged_decode", "fa_paged_reduce", "fa_paged_workspace_bytes", "fa_paged_trace_blocks",
-    "fa_paged_attention_noalloc",
+    "fa_paged_attention_noalloc", "fa_dropout_mask",
     "fa_device_status", "fa_status_string", "fa_version",
 )
 
@@ -34,7 +34,9 @@ class Tensor4(ctypes.Structure):
 class FlashShape(ctypes.Structure):
     _fields_ = [("dtype", ctypes.c_int32), ("B", ctypes.c_int32), ("H", ctypes.c_int32),
                 ("Hk", ctypes.c_int32), ("M", ctypes.c_int32), ("N", ctypes.c_int32),
-                ("D", ctypes.c_int32), ("causal", ctypes.c_int32), ("sm_scale", ctypes.c_float)]
+                ("D", ctypes.c_int32), ("causal", ctypes.c_int32), ("sm_scale", ctypes.c_float),
+                ("dropout_p", ctypes.c_float), ("philox_seed", ctypes.c_uint64),
+                ("philox_offset", ctypes.c_uint64)]
 
 
 class PagedArgs(ctypes.Structure):
@@ -120,8 +122,9 @@ def stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
-def flash_shape(dtype, B, H, Hk, M, N, D, causal, sm_scale):
-    return FlashShape(dtype_code(dtype), B, H, Hk, M, N, D, 1 if causal else 0, float(sm_scale))
+def flash_shape(dtype, B, H, Hk, M, N, D, causal, sm_scale, dropout_p=0.0, seed=0, offset=0):
+    return FlashShape(dtype_code(dtype), B, H, Hk, M, N, D, 1 if causal else 0, float(sm_scale),
+                      float(dropout_p), int(seed) & (2 ** 64 - 1), int(offset) & (2 ** 64 - 1))
 
 
 def byref(x):

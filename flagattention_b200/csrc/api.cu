@@ -1,9 +1,18 @@
 // Status strings, build identification and the device status word.
 #include <cuda_runtime.h>
 
+#include "attn_params.cuh"
 #include "flagattn_b200.h"
 
 namespace fa {
+
+__global__ void dropout_mask_kernel(uint8_t *mask, uint64_t total, float dropout_p, uint64_t seed,
+                                    uint64_t offset) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (uint64_t)gridDim.x * blockDim.x)
+    mask[i] = dropout_keep(seed, offset, i, dropout_p) ? 1 : 0;
+}
+
 
 // Written by a kernel whose bounded wait ran out (the code says which wait);
 // zero in normal operation.  One word per device, inside the library image.
@@ -32,6 +41,17 @@ extern "C" const char *fa_status_string(int status) {
 }
 
 extern "C" const char *fa_version(void) { return "flagattn_b200 1 sm_100a"; }
+
+extern "C" int fa_dropout_mask(int32_t B, int32_t H, int32_t M, int32_t N, float dropout_p,
+                               uint64_t philox_seed, uint64_t philox_offset, uint8_t *mask,
+                               void *stream) {
+  if (!mask || B <= 0 || H <= 0 || M <= 0 || N <= 0) return FA_ERR_BAD_ARG;
+  const uint64_t total = (uint64_t)B * H * M * N;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+  fa::dropout_mask_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      mask, total, dropout_p, philox_seed, philox_offset);
+  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
 
 extern "C" int fa_device_status(int32_t *out, int32_t clear) {
   if (!out) return FA_ERR_BAD_ARG;

@@ -24,6 +24,9 @@ struct FwdParams {
   int causal;
   int w;  // piecewise distance threshold
   float sm_scale;
+  // dropout (flash forward only): keep iff uniform(seed, offset + linear index) > dropout_p
+  float dropout_p;
+  uint64_t seed, offset;
   // split-KV
   int num_splits, n_split_size;
   float *o_partial;    // (B,H,S,M,D)
@@ -40,7 +43,36 @@ struct BwdParams {
   int causal;
   int w;
   float sm_scale;
+  float dropout_p;
+  uint64_t seed, offset;
 };
+
+// First output word of Philox-4x32 with 6 rounds, counter (c0, c1, 0, 0), key (k0, k1).
+__host__ __device__ __forceinline__ uint32_t philox4x32_6(uint32_t k0, uint32_t k1, uint32_t c0,
+                                                          uint32_t c1) {
+  uint32_t c2 = 0, c3 = 0;
+#pragma unroll
+  for (int r = 0; r < 6; ++r) {
+    const uint32_t a0 = c0, a2 = c2;
+    const uint64_t pb = (uint64_t)0xCD9E8D57u * a2, pa = (uint64_t)0xD2511F53u * a0;
+    c0 = (uint32_t)(pb >> 32) ^ c1 ^ k0;
+    c2 = (uint32_t)(pa >> 32) ^ c3 ^ k1;
+    c1 = (uint32_t)pb;
+    c3 = (uint32_t)pa;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+// Dropout decision of attention element `idx` (= ((b*H + h)*M + m)*N + n): true = keep.
+__host__ __device__ __forceinline__ bool dropout_keep(uint64_t seed, uint64_t offset, uint64_t idx,
+                                                      float dropout_p) {
+  const uint64_t ctr = offset + idx;
+  int32_t x = (int32_t)philox4x32_6((uint32_t)seed, (uint32_t)(seed >> 32), (uint32_t)ctr,
+                                    (uint32_t)(ctr >> 32));
+  if (x < 0) x = -x - 1;
+  return (float)x * 4.6566127342e-10f > dropout_p;
+}
 
 template <typename T>
 __device__ __forceinline__ const T *row_ptr(const void *base, const Strides &s, int b, int h,

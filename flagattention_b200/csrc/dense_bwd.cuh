@@ -235,16 +235,34 @@ __global__ void __launch_bounds__(BN / 16 * 32) dense_bwd_dkdv_kernel(const BwdP
         }
       }
 
+      // dropout: keep[j][e] * 1/(1-p) multiplies P on its way into dV and dP on its way into dS
+      const bool dropout = !PW && p.dropout_p > 0.f;
+      const float rp = dropout ? 1.f / (1.f - p.dropout_p) : 1.f;
+      uint32_t keep_bits = 0xffffffffu;  // bit j*4+e
+      if (dropout) {
+        const int hq = hk * G + it / tiles;
+        keep_bits = 0;
+#pragma unroll
+        for (int j = 0; j < BM / 8; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = key_g[e >> 1], qm = m0 + j * 8 + 2 * t4 + (e & 1);
+            const uint64_t idx = (((uint64_t)b * p.H + hq) * p.M + qm) * p.N + key;
+            if (dropout_keep(p.seed, p.offset, idx, p.dropout_p)) keep_bits |= 1u << (j * 4 + e);
+          }
+      }
+      auto kept = [&](int j, int e, float v) { return (keep_bits >> (j * 4 + e)) & 1u ? v * rp : 0.f; };
+
       // dV += P^T dO   (in the far pass, straddling tiles were already counted)
       const bool do_dv = !PW || pass == 0 || !c.need1;
       if (do_dv) {
 #pragma unroll
         for (int kj = 0; kj < BM / 16; ++kj) {
           uint32_t a[4];
-          a[0] = Elem<T>::pack(s[2 * kj][0], s[2 * kj][1]);
-          a[1] = Elem<T>::pack(s[2 * kj][2], s[2 * kj][3]);
-          a[2] = Elem<T>::pack(s[2 * kj + 1][0], s[2 * kj + 1][1]);
-          a[3] = Elem<T>::pack(s[2 * kj + 1][2], s[2 * kj + 1][3]);
+          a[0] = Elem<T>::pack(kept(2 * kj, 0, s[2 * kj][0]), kept(2 * kj, 1, s[2 * kj][1]));
+          a[1] = Elem<T>::pack(kept(2 * kj, 2, s[2 * kj][2]), kept(2 * kj, 3, s[2 * kj][3]));
+          a[2] = Elem<T>::pack(kept(2 * kj + 1, 0, s[2 * kj + 1][0]), kept(2 * kj + 1, 1, s[2 * kj + 1][1]));
+          a[3] = Elem<T>::pack(kept(2 * kj + 1, 2, s[2 * kj + 1][2]), kept(2 * kj + 1, 3, s[2 * kj + 1][3]));
 #pragma unroll
           for (int dj = 0; dj < D / 16; ++dj) {
             uint32_t bb[4];
@@ -279,7 +297,7 @@ __global__ void __launch_bounds__(BN / 16 * 32) dense_bwd_dkdv_kernel(const BwdP
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float dl = (e & 1) ? d2.y : d2.x;
-          float ds = s[j][e] * (dp[j][e] - dl);
+          float ds = s[j][e] * (kept(j, e, dp[j][e]) - dl);
           if (PW) {
             const int key = key_g[e >> 1], qm = m0 + j * 8 + 2 * t4 + (e & 1);
             const bool far = qm + p_seq - key >= p.w;
@@ -549,6 +567,19 @@ __global__ void __launch_bounds__(BM / 16 * 32) dense_bwd_dq_kernel(const BwdPar
           Elem<T>::mma(dp[2 * nj], a, bb[0], bb[1]);
           Elem<T>::mma(dp[2 * nj + 1], a, bb[2], bb[3]);
         }
+      }
+
+      // dropout: dP is masked and scaled like the probabilities were in the forward pass
+      if (!PW && p.dropout_p > 0.f) {
+        const float rp = 1.f / (1.f - p.dropout_p);
+#pragma unroll
+        for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int row = row_g[e >> 1], col = n0 + j * 8 + 2 * t4 + (e & 1);
+            const uint64_t idx = (((uint64_t)b * p.H + h) * p.M + row) * p.N + col;
+            dp[j][e] = dropout_keep(p.seed, p.offset, idx, p.dropout_p) ? dp[j][e] * rp : 0.f;
+          }
       }
 
       // dS, routed to this pass's branch

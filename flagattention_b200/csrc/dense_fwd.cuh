@@ -189,6 +189,18 @@ __global__ void __launch_bounds__(BM / 16 * 32) dense_fwd_kernel(const FwdParams
       }
     }
 
+    // dropout acts on the probabilities that enter P V; the row sums above stay undropped
+    if (!SPLIT && p.dropout_p > 0.f) {
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = row_g[e >> 1], col = n0 + j * 8 + 2 * t4 + (e & 1);
+          const uint64_t idx = (((uint64_t)b * p.H + h) * p.M + row) * p.N + col;
+          if (!dropout_keep(p.seed, p.offset, idx, p.dropout_p)) s[j][e] = 0.f;
+        }
+    }
+
     // O += P V
 #pragma unroll
     for (int kj = 0; kj < BN / 16; ++kj) {
@@ -215,6 +227,7 @@ __global__ void __launch_bounds__(BM / 16 * 32) dense_fwd_kernel(const FwdParams
   for (int i = 0; i < 2; ++i) {
     float l = quad_sum(l_i[i]);
     inv[i] = l > 0.f ? 1.f / l : 0.f;
+    if (!SPLIT && p.dropout_p > 0.f) inv[i] *= 1.f / (1.f - p.dropout_p);
     lse[i] = l > 0.f ? m_i[i] * kLn2 + logf(l) : -INFINITY;
   }
 

@@ -13,6 +13,7 @@ inline int validate_shape(const fa_flash_shape *s) {
   if (s->H % s->Hk != 0) return FA_ERR_BAD_ARG;
   if (!(s->D == 16 || s->D == 32 || s->D == 64 || s->D == 128)) return FA_ERR_UNSUPPORTED;
   if ((int64_t)s->B * s->H > 65535) return FA_ERR_TOO_LARGE;  // grid.y / grid.z limit
+  if (!(s->dropout_p >= 0.f && s->dropout_p < 1.f)) return FA_ERR_BAD_ARG;
   return FA_OK;
 }
 

@@ -124,6 +124,7 @@ static BwdParams make_bwd(const fa_flash_shape *s, const fa_tensor4 *q, const fa
   p.lse = lse, p.delta = delta;
   p.B = s->B, p.H = s->H, p.Hk = s->Hk, p.M = s->M, p.N = s->N;
   p.causal = s->causal, p.sm_scale = s->sm_scale;
+  p.dropout_p = s->dropout_p, p.seed = s->philox_seed, p.offset = s->philox_offset;
   return p;
 }
 

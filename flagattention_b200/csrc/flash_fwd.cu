@@ -58,6 +58,7 @@ static FwdParams make_fwd_params(const fa_flash_shape *s, const fa_tensor4 *q, c
   p.sq = strides_of(q), p.sk = strides_of(k), p.sv = strides_of(v);
   p.B = s->B, p.H = s->H, p.Hk = s->Hk, p.M = s->M, p.N = s->N;
   p.causal = s->causal, p.sm_scale = s->sm_scale;
+  p.dropout_p = s->dropout_p, p.seed = s->philox_seed, p.offset = s->philox_offset;
   p.num_splits = 1;
   return p;
 }
@@ -90,6 +91,7 @@ extern "C" int fa_splitkv_fwd(const fa_flash_shape *s, const fa_tensor4 *q, cons
   if (int st = validate_shape(s)) return st;
   if (int st = validate_tensors({q, k, v})) return st;
   if (!o_partial || !lse_partial) return FA_ERR_WORKSPACE;
+  if (s->dropout_p > 0.f) return FA_ERR_UNSUPPORTED;  // no dropout on the split-KV path
   if (num_splits < 1 || num_splits > 65535 || n_split_size <= 0 ||
       n_split_size % SplitTile::BN != 0)
     return FA_ERR_BAD_ARG;

@@ -73,7 +73,8 @@ static int launch_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, const fa_te
 }
 
 static bool covered(const fa_flash_shape *s) {
-  return !generic_forced() && s->sm_scale > 0.f && (s->D == 64 || s->D == 128);
+  return !generic_forced() && s->sm_scale > 0.f && (s->D == 64 || s->D == 128) &&
+         s->dropout_p == 0.f;  // dropout runs on the shape-generic kernels
 }
 
 // Return FA_OK / a negative status, or 1 when the tensor-core path does not cover the call.

@@ -11,6 +11,7 @@ import math
 import torch
 
 from . import _C
+from .dropout import philox_cuda_seed_offset
 from .split_kv import get_fwd_config as get_fwd_config_kv_split
 from .split_kv import num_splits_herustic, _splitkv_forward
 
@@ -21,21 +22,21 @@ def get_fwd_config(B, H, M, N, D, causal):
     """Tile shape used by the one-pass forward kernel: (BLOCK_M, BLOCK_N, stages, warps).
     Kept for interface compatibility (src/flag_attn/flash.py:290-322); the tile
     shape is compiled into the kernels, so overriding this has no effect."""
-    return (128, 64, 2, 8)
+    return (128, 64, 2, 6)
 
 
 def get_bwd_config(B, H, M, N, D, causal):
     """Counterpart of src/flag_attn/flash.py:493-519; informational only."""
-    return (64, 128, 2, 8)
+    return (128, 128, 3, 18)
 
 
-def _forward(q, k, v, causal, sm_scale):
+def _forward(q, k, v, causal, sm_scale, dropout_p=0.0, seed=0, offset=0):
     B, H, M, D = q.shape
     N, Hk = k.shape[2], k.shape[1]
     lib = _C.load()
     o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     L = torch.empty((B, H, M), device=q.device, dtype=torch.float32)
-    shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
+    shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale, dropout_p, seed, offset)
     tq, tk, tv, to = _C.tensor4(q), _C.tensor4(k), _C.tensor4(v), _C.tensor4(o)
     st = lib.fa_flash_fwd(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv), _C.byref(to),
                           _C.fptr(L), _C.stream_ptr(q.device))
@@ -56,7 +57,7 @@ def _total_attention(q, k, L, causal, sm_scale):
     return tot
 
 
-def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None):
+def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None, dropout_p=0.0, seed=0, offset=0):
     """Launches delta, dK/dV and dQ. `mark(name)`, when given, is called before the first launch
     and after each one (the benchmark records CUDA events there)."""
     B, H, M, D = q.shape
@@ -65,7 +66,7 @@ def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None):
     do = _C.kernel_ready(do)
     with torch.cuda.device(q.device):
         stream = _C.stream_ptr(q.device)
-        shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale)
+        shape = _C.flash_shape(q.dtype, B, H, Hk, M, N, D, causal, sm_scale, dropout_p, seed, offset)
         delta = torch.empty_like(L)
         # dk / dv come out with Hk heads: the group sum is done in the kernel
         dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=q.device)
@@ -101,7 +102,7 @@ class FlashAttention(torch.autograd.Function):
         Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
         assert Dq == Dk == Dv, "feature size of q, k, v should be equal"
         assert Dk in {16, 32, 64, 128}
-        assert dropout_p == 0.0, "dropout is not implemented by the B200 kernels"
+        assert 0.0 <= dropout_p < 1.0, f"dropout_p={dropout_p}"
         assert q.is_cuda and k.is_cuda and v.is_cuda, "inputs must be CUDA tensors"
         assert q.dtype == k.dtype == v.dtype
 
@@ -117,13 +118,21 @@ class FlashAttention(torch.autograd.Function):
         q, k, v = _C.kernel_ready(q), _C.kernel_ready(k), _C.kernel_ready(v)
 
         with torch.cuda.device(q.device):
+            # dropout: one Philox counter per element of the (B, H, M, N) attention matrix
+            is_dropout = dropout_p > 0
+            if is_dropout:
+                seed, offset = philox_cuda_seed_offset(B * H * M * N, q.device)
+            else:
+                seed, offset = 0, 0
+
             num_sms = torch.cuda.get_device_properties(q.device).multi_processor_count
             cfg = get_fwd_config_kv_split(B, H, M, N, D, causal)
             S = num_splits_herustic(B, H, M, N, cfg[0], cfg[1], num_sms, 128)
             if S > 1:
+                assert not is_dropout, "Cannot apply dropout with splitkv."
                 o, L = _splitkv_forward(q, k, v, causal, sm_scale, S)
             else:
-                o, L = _forward(q, k, v, causal, sm_scale)
+                o, L = _forward(q, k, v, causal, sm_scale, dropout_p, seed, offset)
             tot_attn = None
             if return_total_attention:
                 tot_attn = _total_attention(q, k, L, causal, sm_scale)
@@ -131,17 +140,22 @@ class FlashAttention(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, o, L)
         ctx.sm_scale = sm_scale
         ctx.causal = causal
+        ctx.dropout_p = dropout_p
+        ctx.seed = seed
+        ctx.offset = offset
 
         has_extra_return = True in (return_log_normalizer, return_total_attention, return_seed_offset)
         if has_extra_return:
-            # seed / offset are only produced with dropout, which is not built
-            return (o, L if return_log_normalizer else None, tot_attn, None, None)
+            return (o, L if return_log_normalizer else None, tot_attn,
+                    seed if is_dropout and return_seed_offset else None,
+                    offset if is_dropout and return_seed_offset else None)
         return o
 
     @staticmethod
     def backward(ctx, do, *ignored):
         q, k, v, o, L = ctx.saved_tensors
-        dq, dk, dv = _backward(q, k, v, o, L, do, ctx.causal, ctx.sm_scale)
+        dq, dk, dv = _backward(q, k, v, o, L, do, ctx.causal, ctx.sm_scale, None, ctx.dropout_p,
+                               ctx.seed, ctx.offset)
         return dq, dk, dv, None, None, None, None, None, None
 
 
@@ -154,9 +168,10 @@ def attention(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
            fp16 or bf16 CUDA tensors, heads_q a multiple of heads_k, headdim in {16,32,64,128}.
         causal: bottom-right aligned causal mask.
         sm_scale: softmax scale, default 1/sqrt(headdim).
-        dropout_p: must be 0.0 (dropout is not built).
-        return_log_normalizer / return_total_attention / return_seed_offset: when any is
-           set, returns (out, log_normalizer | None, total_attention | None, None, None).
+        dropout_p: dropout probability on the attention weights.
+        return_log_normalizer / return_total_attention / return_seed_offset: when any is set,
+           returns (out, log_normalizer | None, total_attention | None, seed | None, offset | None);
+           seed and offset are the Philox seed and starting offset used by dropout (None without).
 
     Returns out, shape of q; log_normalizer (batch, heads_q, seqlen_q) fp32;
     total_attention (batch, heads_q, seqlen_k) fp32.

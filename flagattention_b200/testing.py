@@ -11,7 +11,9 @@ import math
 
 import torch
 
-__all__ = ["flash_attention", "piecewise_attention", "paged_attention"]
+from .dropout import recompute_mask  # noqa: F401
+
+__all__ = ["flash_attention", "piecewise_attention", "paged_attention", "recompute_mask"]
 
 
 def _causal_mask(m, n, device):
@@ -20,7 +22,6 @@ def _causal_mask(m, n, device):
 
 def flash_attention(q, k, v, causal, dropout_p=0.0, dropout_mask=None, sm_scale=None,
                     return_log_normalizer=False, return_total_attention=False, upcast=False):
-    assert dropout_p == 0.0 and dropout_mask is None, "dropout is not built"
     dtype = q.dtype
     if upcast:
         q, k, v = q.float(), k.float(), v.float()
@@ -36,10 +37,12 @@ def flash_attention(q, k, v, causal, dropout_p=0.0, dropout_mask=None, sm_scale=
     p = torch.softmax(s, dim=-1, dtype=torch.float32)
     if causal:
         p = p.masked_fill(~keep, 0.0)
-    o = torch.matmul(p.to(v.dtype), v).to(dtype)
+    tot = p.sum(dim=-2) if return_total_attention else None
+    if dropout_mask is not None:
+        p = p.masked_fill(~dropout_mask, 0.0)
+    o = (torch.matmul(p.to(v.dtype), v) * (1.0 / (1 - dropout_p))).to(dtype)
     if return_log_normalizer or return_total_attention:
-        return (o, torch.logsumexp(s, dim=-1) if return_log_normalizer else None,
-                p.sum(dim=-2) if return_total_attention else None)
+        return (o, torch.logsumexp(s, dim=-1) if return_log_normalizer else None, tot)
     return o
 
 

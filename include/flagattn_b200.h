@@ -59,6 +59,13 @@ typedef struct fa_flash_shape {
   int32_t B, H, Hk, M, N, D;
   int32_t causal;
   float sm_scale;
+  /* Dropout on the attention probabilities (flash_attention only; 0 disables it).  Element
+   * (b, h, m, n) is kept iff u > dropout_p, u = the first output of Philox-4x32 with 6 rounds,
+   * key = philox_seed, counter = philox_offset + ((b*H + h)*M + m)*N + n, mapped to [0, 1);
+   * kept probabilities are scaled by 1 / (1 - dropout_p).  Mirrors src/flag_attn/flash.py:52-57,
+   * 454-457, 697-721, 877-880; the split-KV entry points reject dropout as the reference does. */
+  float dropout_p;
+  uint64_t philox_seed, philox_offset;
 } fa_flash_shape;
 
 /* Forward: o = softmax(sm_scale * q k^T [+causal]) v, lse = natural-log
@@ -114,6 +121,12 @@ int fa_flash_bwd_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, const fa_ten
 int fa_flash_bwd_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
                     const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                     const float *delta, const fa_tensor4 *dq, void *stream);
+
+/* Regenerates the dropout keep-mask of a flash_attention call: mask[b,h,m,n] (1 byte each,
+ * contiguous) = 1 iff the element was kept.  Replaces `recompute_mask_kernel`
+ * (src/flag_attn/testing/dropout.py:5-25). */
+int fa_dropout_mask(int32_t B, int32_t H, int32_t M, int32_t N, float dropout_p,
+                    uint64_t philox_seed, uint64_t philox_offset, uint8_t *mask, void *stream);
 
 /* ---------------------------------------------------------------------- */
 /* piecewise_attention                                                     */

@@ -6,7 +6,8 @@ scores (:39), bottom-right causal fill with -inf (:33,:40-41), scores to fp32
 (:43), logsumexp (:44-45), fp32 softmax (:48), re-masking so rows without a
 visible key become zero (:49-50), column sums (:52-53), P cast to v's dtype
 before P@V (:60), output cast back to the input dtype (:61).
-Dropout is not restated (outside this build's scope).
+Dropout follows :55-60 there: the keep-mask is an input, dropped probabilities are zeroed after the
+column sums and before P@V, and the result is scaled by 1 / (1 - dropout_p).
 """
 import math
 
@@ -14,7 +15,7 @@ import torch
 
 
 def flash_attention(q, k, v, causal, sm_scale=None, return_log_normalizer=False,
-                    return_total_attention=False, upcast=False):
+                    return_total_attention=False, upcast=False, dropout_p=0.0, dropout_mask=None):
     in_dtype = q.dtype
     if upcast:
         q, k, v = q.float(), k.float(), v.float()
@@ -41,7 +42,9 @@ def flash_attention(q, k, v, causal, sm_scale=None, return_log_normalizer=False,
     if causal:
         probs = torch.where(visible, probs, 0.0)
     total = probs.sum(dim=-2) if return_total_attention else None
-    out = (probs.to(v.dtype) @ v).to(in_dtype)
+    if dropout_mask is not None:
+        probs = probs.masked_fill(~dropout_mask, 0.0)
+    out = ((probs.to(v.dtype) @ v) * (1.0 / (1 - dropout_p))).to(in_dtype)
     if return_log_normalizer or return_total_attention:
         return out, lse, total
     return out

@@ -100,3 +100,24 @@ def test_paged_oracle_matches_reference(idx, impl):
     o = impl(c["q"], c["key_cache"], c["value_cache"], c["block_tables"], c["context_lens"], c["scale"])
     assert o.dtype == c["out"].dtype
     assert max_diff(o, c["out"]) <= 1e-6 + 2 ** -11 * c["out"].float().abs().max().item()
+
+
+# ---- dropout random stream: oracle/dropout.py against the reference's mask kernel ----------------
+def _philox_golden():
+    return torch.load(os.path.join(GOLDEN, "philox.pt"))
+
+
+def test_philox_uniform_matches_triton_rand():
+    import numpy as np
+    from oracle.dropout import philox_uniform
+    for r in _philox_golden()["rands"]:
+        ctr = np.arange(r["values"].numel(), dtype=np.uint64) + np.uint64(r["offset"])
+        assert np.array_equal(philox_uniform(r["seed"], ctr), r["values"].numpy())   # bit-exact
+
+
+def test_dropout_mask_matches_reference_kernel():
+    import numpy as np
+    from oracle.dropout import dropout_mask
+    for c in _philox_golden()["masks"]:
+        mine = dropout_mask(c["B"], c["H"], c["M"], c["N"], c["p"], c["seed"], c["offset"])
+        assert np.array_equal(mine, c["mask"].numpy())

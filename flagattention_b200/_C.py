@@ -22,6 +22,7 @@ EXPORTED_SYMBOLS = (
     "fa_flash_bwd_dq", "fa_piecewise_fwd", "fa_piecewise_bwd_dkdv", "fa_piecewise_bwd_dq",
     "fa_paged_decode", "fa_paged_reduce", "fa_paged_workspace_bytes", "fa_paged_trace_blocks",
     "fa_paged_attention_noalloc", "fa_dropout_mask",
+    "fa_flash_bwd_fused", "fa_flash_bwd_fused_workspace_bytes",
     "fa_device_status", "fa_status_string", "fa_version",
 )
 
@@ -78,6 +79,7 @@ def load():
             lib.fa_version.restype = ctypes.c_char_p
             lib.fa_splitkv_workspace_bytes.restype = ctypes.c_int64
             lib.fa_paged_workspace_bytes.restype = ctypes.c_int64
+            lib.fa_flash_bwd_fused_workspace_bytes.restype = ctypes.c_int64
             lib.fa_num_splits_heuristic.restype = ctypes.c_int32
             lib.fa_num_splits_heuristic.argtypes = [ctypes.c_int32] * 8
             _lib = lib

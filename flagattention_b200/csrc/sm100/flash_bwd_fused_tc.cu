@@ -1,0 +1,99 @@
+// Launcher and C entry points of the one-pass tcgen05 flash_attention backward.
+#include <cstdlib>
+
+#include "flash_bwd_fused_tc.cuh"
+#include "tma_host.cuh"
+#include "../common.cuh"
+#include "../dense_host.cuh"
+
+namespace fa {
+int *device_status_word();
+
+namespace tc {
+
+bool generic_forced();
+
+// FLAGATTN_B200_BWD_TWO_KERNELS=1 turns the one-pass kernel off (the tests cross-check both).
+static bool fused_disabled() {
+  const char *e = std::getenv("FLAGATTN_B200_BWD_TWO_KERNELS");
+  return e && e[0] == '1';
+}
+
+static bool fused_covered(const fa_flash_shape *s) {
+  return !generic_forced() && !fused_disabled() && s->sm_scale > 0.f &&
+         (s->D == 64 || s->D == 128) && s->dropout_p == 0.f;
+}
+
+static int64_t fused_workspace_bytes(const fa_flash_shape *s) {
+  const int64_t mpad = ((int64_t)s->M + 127) / 128 * 128;
+  return (int64_t)s->B * s->H * mpad * s->D * 4;
+}
+
+template <typename T, int D>
+static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                        const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                        const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
+                        const fa_tensor4 *dv, float *workspace, cudaStream_t stream) {
+  using C = FusedBwdCfg<D>;
+  CUtensorMap mq, mdo, mk, mv;
+  if (!make_map_bhld(&mq, q, s->dtype, s->B, s->H, s->M, D, C::BM) ||
+      !make_map_bhld(&mdo, d_o, s->dtype, s->B, s->H, s->M, D, C::BM) ||
+      !make_map_bhld(&mk, k, s->dtype, s->B, s->Hk, s->N, D, C::BN) ||
+      !make_map_bhld(&mv, v, s->dtype, s->B, s->Hk, s->N, D, C::BN))
+    return FA_ERR_UNSUPPORTED;
+  auto kern = flash_bwd_fused_tc_kernel<T, D>;
+  static unsigned long long done = 0;
+  if (int st = ensure_dyn_smem(kern, C::kTotal, &done)) return st;
+  FusedBwdParams fp{};
+  BwdTcParams &p = fp.base;
+  p.lse = lse, p.delta = delta;
+  p.B = s->B, p.H = s->H, p.Hk = s->Hk, p.M = s->M, p.N = s->N;
+  p.causal = s->causal, p.sm_scale = s->sm_scale;
+  p.status = device_status_word();
+  p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
+  fp.dq_acc = workspace;
+  fp.Mpad = (s->M + 127) / 128 * 128;
+  if (cudaMemsetAsync(workspace, 0, (size_t)fused_workspace_bytes(s), stream) != cudaSuccess)
+    return FA_ERR_LAUNCH;
+  dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
+  kern<<<grid, kBwdThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, fp);
+  FA_CHECK_LAUNCH();
+  dim3 cgrid((s->M + 31) / 32, s->H, s->B);
+  dq_convert_kernel<T, D><<<cgrid, 256, 0, stream>>>(workspace, dq->ptr, strides_of(dq), s->H,
+                                                     s->M, fp.Mpad, s->sm_scale);
+  FA_CHECK_LAUNCH();
+  return FA_OK;
+}
+
+}  // namespace tc
+}  // namespace fa
+
+using namespace fa;
+
+extern "C" int64_t fa_flash_bwd_fused_workspace_bytes(const fa_flash_shape *s) {
+  if (!s || validate_shape(s) != FA_OK || !tc::fused_covered(s)) return 0;
+  return tc::fused_workspace_bytes(s);
+}
+
+extern "C" int fa_flash_bwd_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                                  const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                                  const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
+                                  const fa_tensor4 *dv, void *workspace, int64_t workspace_bytes,
+                                  void *stream) {
+  if (int st = validate_shape(s)) return st;
+  if (int st = validate_tensors({q, k, v, d_o, dq, dk, dv})) return st;
+  if (!lse || !delta) return FA_ERR_BAD_ARG;
+  if (!tc::fused_covered(s)) return FA_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < tc::fused_workspace_bytes(s) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return FA_ERR_WORKSPACE;
+  float *ws = static_cast<float *>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define FA_FUSED_ARGS s, q, k, v, d_o, lse, delta, dq, dk, dv, ws, st
+  if (s->dtype == FA_F16)
+    return s->D == 128 ? tc::launch_fused<__half, 128>(FA_FUSED_ARGS)
+                       : tc::launch_fused<__half, 64>(FA_FUSED_ARGS);
+  return s->D == 128 ? tc::launch_fused<__nv_bfloat16, 128>(FA_FUSED_ARGS)
+                     : tc::launch_fused<__nv_bfloat16, 64>(FA_FUSED_ARGS);
+#undef FA_FUSED_ARGS
+}

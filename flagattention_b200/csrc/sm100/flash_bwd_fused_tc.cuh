@@ -1,0 +1,531 @@
+// flash_attention backward on tcgen05 in ONE pass over the score tiles (head_dim 64 and 128):
+// dK, dV and dQ come out of the same kernel, so S and dP are computed once (five GEMMs per
+// 128 x 128 tile) instead of once in a dK/dV kernel and again in a dQ kernel (seven).
+//
+// One CTA per 128 keys walks the query tiles (and the query heads of its GQA group).  dK and dV
+// accumulate in TMEM for the whole walk.  The dQ contribution of a tile, dS K, is a complete
+// 128 x D product of its own: it is accumulated in TMEM for the tile, read back by the
+// element-wise warps and added into an fp32 workspace in global memory with vector reductions
+// (`red.global.add.v4.f32`); a small kernel scales and converts the workspace afterwards.  The
+// order of those additions is not fixed, so dQ is reproducible only to fp32 rounding.
+//
+//   warp 0       TMA producer
+//   warp 1       MMA issuer (one thread); every MMA is 128 x 128 x 16 (128 x 64 x 16 at D = 64)
+//   warps 2..17  element-wise stage, one thread per (accumulator row, 32 columns)
+//
+// TMEM (512 columns):  S^T / P^T | dP^T, then dQ | dK | dV.
+// Shared memory:       K, V resident | Q ring | dO ring | dS^T (16-bit, 128-byte swizzle).
+// dS^T is written once to shared memory and read by two GEMMs under two descriptors: as the
+// K-major A operand of dK += dS^T Q and as the MN-major A operand of dQ = dS K.
+//
+// Issue order of a tile (tensor pipe, in order):   dV(t) | S^T(t+1) | dQ(t) | dK(t) | dP^T(t+1)
+// Element-wise order:                              phase 2 (t) | phase 1 (t+1) with the dQ(t) read-out woven in
+//   phase 1: P^T = exp2(S^T * scale - L), written over S^T (TMEM A operand of dV += P^T dO)
+//   phase 2: dS^T = P^T * (dP^T - delta), written to shared memory
+#pragma once
+
+#include "flash_bwd_tc.cuh"
+
+namespace fa {
+namespace tc {
+
+template <int D>
+struct FusedBwdCfg {
+  static constexpr int BM = 128, BN = 128, NQ = 3, NDO = (D == 128 ? 1 : 2);
+  static constexpr int KSUB = D / 64;
+  static constexpr int kTile = 128 * D * 2;            // any 128-row operand tile
+  static constexpr int kK = 0;
+  static constexpr int kV = kTile;
+  static constexpr int kQ0 = 2 * kTile;                // Q ring
+  static constexpr int kDO0 = kQ0 + NQ * kTile;        // dO ring
+  static constexpr int kDS = kDO0 + NDO * kTile;       // dS^T: 128 key rows x 128 queries x 2 B
+  static constexpr int kDsBytes = 128 * 128 * 2;
+  static constexpr int kBars = kDS + kDsBytes;
+  static constexpr int kMisc = kBars + 24 * 8;
+  static constexpr int kTotal = kMisc + 16 + 1024;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColS = 0, kColB = 128, kColDK = 256, kColDV = 256 + D;
+  static_assert(kTotal <= 232448, "shared memory budget");
+};
+
+enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 4, FB_DO_FULL = 7, FB_DO_FREE = 9,
+                FB_S_FULL = 11, FB_DP_FULL = 12, FB_P1 = 13, FB_P2 = 14, FB_DQ_FULL = 15,
+                FB_DQ_FREE = 16, FB_DS_FREE = 17, FB_DONE = 18 };
+
+struct FusedBwdParams {
+  BwdTcParams base;
+  float *dq_acc;   // (B, H, D / 4, Mpad, 4) fp32, zeroed before the launch
+  int Mpad;        // M rounded up to a multiple of 128
+};
+
+__device__ __forceinline__ void red_add_v4(float *dst, uint32_t a, uint32_t b, uint32_t c,
+                                           uint32_t d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst), "f"(__uint_as_float(a)),
+               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    flash_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                              const __grid_constant__ CUtensorMap map_do,
+                              const __grid_constant__ CUtensorMap map_k,
+                              const __grid_constant__ CUtensorMap map_v, const FusedBwdParams fp) {
+  using C = FusedBwdCfg<D>;
+  constexpr int BM = C::BM, BN = C::BN, KSUB = C::KSUB, NQ = C::NQ, NDO = C::NDO;
+  const BwdTcParams &p = fp.base;
+  extern __shared__ uint8_t smem_unaligned[];
+  const uint32_t smem = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_unaligned + (smem - smem_u32(smem_unaligned));
+  auto bar = [&](int i) { return smem + C::kBars + i * 8; };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + C::kMisc);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + C::kMisc + 8);
+  const AbortCtx actx{abort_flag, p.status};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.Hk;
+  const int n0 = nb * BN;
+  const int p_seq = p.N - p.M;
+  const int num_m_tiles = (p.M + BM - 1) / BM;
+  int mt_lo = 0;
+  if (p.causal) mt_lo = max(0, n0 - p_seq) / BM;
+  int mt_hi = num_m_tiles;
+  if (p.mode == 1) {  // query tiles that hold a near pair
+    const int lim = p.w - p_seq + n0 + BN - 1;
+    mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+  } else if (p.mode == 2) {  // query tiles that hold a far pair
+    const int lim = p.w - p_seq + n0 - (BM - 1);
+    mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+  }
+  const int tiles = max(0, mt_hi - mt_lo);
+  const int T_tiles = tiles * G;
+
+  if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(FB_KV_FULL), 1);
+    for (int s = 0; s < NQ; ++s) {
+      mbar_init(bar(FB_Q_FULL + s), 1);
+      mbar_init(bar(FB_Q_FREE + s), 1);
+    }
+    for (int s = 0; s < NDO; ++s) {
+      mbar_init(bar(FB_DO_FULL + s), 1);
+      mbar_init(bar(FB_DO_FREE + s), 1);
+    }
+    mbar_init(bar(FB_S_FULL), 1);
+    mbar_init(bar(FB_DP_FULL), 1);
+    mbar_init(bar(FB_P1), kEwWarps);
+    mbar_init(bar(FB_P2), kEwWarps);
+    mbar_init(bar(FB_DQ_FULL), 1);
+    mbar_init(bar(FB_DQ_FREE), kEwWarps);
+    mbar_init(bar(FB_DS_FREE), 1);
+    mbar_init(bar(FB_DONE), 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem + C::kMisc, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer -----------------------------------
+    if (lane == 0 && T_tiles > 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_do);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      mbar_expect_tx(bar(FB_KV_FULL), 2 * C::kTile);
+      for (int s = 0; s < KSUB; ++s) {
+        tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, n0, hk, b);
+        tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_KV_FULL), s * 64, n0, hk, b);
+      }
+      int issued_q = 0, issued_do = 0;
+      bool ok = true;
+      int sq = 0, phq = 1, sd = 0, phd = 1;   // slot and the "free" parity to wait for
+      for (int t = 0; t < T_tiles; ++t) {
+        const int h = hk * G + t / tiles, m0 = (mt_lo + t % tiles) * BM;
+        ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 711);
+        if (!ok) break;
+        mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
+        for (int s = 0; s < KSUB; ++s)
+          tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
+                      s * 64, m0, h, b);
+        ++issued_q;
+        ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 712);
+        if (!ok) break;
+        mbar_expect_tx(bar(FB_DO_FULL + sd), C::kTile);
+        for (int s = 0; s < KSUB; ++s)
+          tma_load_4d(smem + C::kDO0 + sd * C::kTile + s * BM * 128, &map_do, bar(FB_DO_FULL + sd),
+                      s * 64, m0, h, b);
+        ++issued_do;
+        if (++sq == NQ) sq = 0, phq ^= 1;
+        if (++sd == NDO) sd = 0, phd ^= 1;
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA gives its shared memory back
+        const long long t0 = clock64();
+        for (int i = max(0, issued_q - NQ); i < issued_q; ++i)
+          while (!mbar_try_wait(bar(FB_Q_FULL + i % NQ), (i / NQ) & 1) && clock64() - t0 < 2000000) {}
+        for (int i = max(0, issued_do - NDO); i < issued_do; ++i)
+          while (!mbar_try_wait(bar(FB_DO_FULL + i % NDO), (i / NDO) & 1) && clock64() - t0 < 2000000) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------
+    if (lane == 0 && T_tiles > 0) {
+      constexpr uint32_t idesc_s = instr_desc_f16(BN, BM, TcElem<T>::kFormat, 0, 0);   // S^T, dP^T
+      constexpr uint32_t idesc_acc = instr_desc_f16(BN, D, TcElem<T>::kFormat, 0, 1);  // dV, dK
+      constexpr uint32_t idesc_dq = instr_desc_f16(BM, D, TcElem<T>::kFormat, 1, 1);   // dQ
+      constexpr uint32_t kTile16 = C::kTile >> 4;
+      const uint32_t k_lo = smem_desc_lo(smem + C::kK, 0), v_lo = smem_desc_lo(smem + C::kV, 0);
+      const uint32_t k_mn_lo = smem_desc_lo(smem + C::kK, BN * 128);     // K as MN-major B of dQ
+      const uint32_t q_k_lo = smem_desc_lo(smem + C::kQ0, 0);            // Q as K-major B operand
+      const uint32_t q_mn_lo = smem_desc_lo(smem + C::kQ0, BM * 128);     // Q as MN-major B operand
+      const uint32_t do_k_lo = smem_desc_lo(smem + C::kDO0, 0);
+      const uint32_t do_mn_lo = smem_desc_lo(smem + C::kDO0, BM * 128);
+      const uint32_t ds_k_lo = smem_desc_lo(smem + C::kDS, 0);            // dS^T as K-major A of dK
+      const uint32_t ds_mn_lo = smem_desc_lo(smem + C::kDS, BN * 128);    // dS as MN-major A of dQ
+      bool ok = mbar_wait(bar(FB_KV_FULL), 0, actx, 811);
+      auto issue_s = [&](int sq, int phq) -> bool {
+        if (!mbar_wait(bar(FB_Q_FULL + sq), phq, actx, 812)) return false;
+        tc_fence_after();
+        const uint32_t b_lo = q_k_lo + sq * kTile16;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
+          mma_ss_lo(tmem + C::kColS, k_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(FB_S_FULL));
+        return true;
+      };
+      auto issue_dp = [&](int sd, int phd) -> bool {
+        if (!mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 813)) return false;
+        tc_fence_after();
+        const uint32_t b_lo = do_k_lo + sd * kTile16;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
+          mma_ss_lo(tmem + C::kColB, v_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(FB_DP_FULL));
+        return true;
+      };
+      if (ok) ok = issue_s(0, 0);
+      if (ok) ok = issue_dp(0, 0);
+      int sq = 0, phq = 0, sd = 0, phd = 0;
+      for (int t = 0; t < T_tiles && ok; ++t) {
+        int nsq = sq + 1, nphq = phq, nsd = sd + 1, nphd = phd;
+        if (nsq == NQ) nsq = 0, nphq ^= 1;
+        if (nsd == NDO) nsd = 0, nphd ^= 1;
+        const uint32_t acc = t > 0 ? 1u : 0u;
+        const uint32_t par = t & 1;
+        // dV += P^T(t) dO(t)
+        ok = mbar_wait(bar(FB_P1), par, actx, 814);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const uint32_t b_lo = do_mn_lo + sd * kTile16;
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk)
+            mma_ts_lo(tmem + C::kColDV, tmem + C::kColS + (kk >> 1) * 32 + (kk & 1) * 8,
+                      b_lo + ((kk * 16 * 128) >> 4), idesc_acc, kk > 0 ? 1u : acc);
+          mma_commit(bar(FB_DO_FREE + sd));
+        }
+        if (t + 1 < T_tiles) ok = issue_s(nsq, nphq);
+        if (!ok) break;
+        ok = mbar_wait(bar(FB_P2), par, actx, 815);
+        if (!ok) break;
+        tc_fence_after();
+        // dQ(t) = dS(t) K, a fresh accumulator over the dP^T columns
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t off16 = (kk * 16 * 128) >> 4;
+          mma_ss_lo(tmem + C::kColB, ds_mn_lo + off16, k_mn_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(FB_DQ_FULL));
+        // dK += dS^T(t) Q(t)
+        {
+          const uint32_t b_lo = q_mn_lo + sq * kTile16;
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk) {
+            const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
+            mma_ss_lo(tmem + C::kColDK, ds_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
+                      kk > 0 ? 1u : acc);
+          }
+          mma_commit(bar(FB_Q_FREE + sq));
+          mma_commit(bar(FB_DS_FREE));
+        }
+        if (t + 1 < T_tiles) {
+          ok = mbar_wait(bar(FB_DQ_FREE), par, actx, 816);   // dQ(t) has been read out
+          if (!ok) break;
+          tc_fence_after();
+          ok = issue_dp(nsd, nphd);
+        }
+        sq = nsq, phq = nphq, sd = nsd, phd = nphd;
+      }
+      if (ok) {
+        mma_commit(bar(FB_DONE));
+        mbar_wait(bar(FB_DONE), 0, actx, 817);
+      }
+    }
+  } else {
+    // ------------------------------ element-wise warps --------------------------
+    const int ew = warp - 2;
+    const int slice = warp & 3, cg = ew >> 2;       // TMEM lane slice, 32-column group
+    const int row = slice * 32 + lane;              // accumulator row of this thread
+    const int key = n0 + row;
+    const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
+    const float qk_scale = p.sm_scale * kLog2e;
+    const bool key_ok = key < p.N;
+    // this thread's 64 bytes of a dS^T row: sub-tile cg / 2, 16-byte chunks (cg & 1) * 4 .. + 3
+    uint8_t *ds_row = smem_gen + C::kDS + (cg >> 1) * (128 * 128) + row * 128;
+    const int ds_chunk0 = (cg & 1) * 4, ds_xor = row & 7;
+    bool ok = true;
+
+    float pv[32];
+    constexpr int QC = D / 4;   // dQ columns of this thread: 32 or 16
+    constexpr int QQ = QC / 4;  // per quarter of phase 1: 8 or 4
+    // Lane c holds lse / delta of query column c of this thread's 32 columns (the loops below
+    // broadcast them with shuffles); queries past M get lse = +inf, which makes their P exactly
+    // zero.  The values of a tile are fetched one tile ahead, so their latency is off the
+    // critical path.
+    float lse_next = INFINITY, dlt_next = 0.f, dlt_lane = 0.f;
+    // (head, query tile) of the tile whose statistics are fetched next, of the next phase 1 and
+    // of the tile in phase 2 / read-out: running counters, no divisions in the loop
+    struct TileIdx {
+      int h, mt;
+    };
+    TileIdx t_fetch{hk * G, mt_lo}, t_p1{hk * G, mt_lo}, t_cur{hk * G, mt_lo};
+    auto advance = [&](TileIdx &x) {
+      if (++x.mt == mt_hi) x.mt = mt_lo, ++x.h;
+    };
+    auto fetch_stats = [&]() {
+      const int qm_lane = t_fetch.mt * BM + cg * 32 + lane;
+      const int64_t li = ((int64_t)b * p.H + t_fetch.h) * p.M + min(qm_lane, p.M - 1);
+      // volatile: the loads must be issued here, a tile ahead of their use
+      asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(lse_next) : "l"(p.lse + li));
+      asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(dlt_next) : "l"(p.delta + li));
+      advance(t_fetch);
+    };
+    if (T_tiles > 0) fetch_stats();
+    // P^T(t) = exp2(S^T * scale - lse) into `pv` and, packed, over S^T in TMEM
+    // With `drain`, the dQ partial of the PREVIOUS tile is read out of TMEM on the way, a quarter
+    // after every quarter of the exponentials, and added to the fp32 workspace (dq_dst; null for
+    // rows past M).  The reductions leave the SM at a fixed rate (about one 32-byte sector per
+    // clock: 64 KB take as long as the GEMMs of a tile), so issued in one burst they stall the
+    // warp for that long; woven into the exponentials part of that time is hidden.
+    auto phase1 = [&](int t, bool drain, float *dq_dst) -> bool {
+      const int m0 = t_p1.mt * BM;
+      advance(t_p1);
+      const bool q_ok = m0 + cg * 32 + lane < p.M;
+      const float lse_lane = q_ok ? lse_next * kLog2e : INFINITY;
+      dlt_lane = q_ok ? dlt_next : 0.f;
+      if (t + 1 < T_tiles) fetch_stats();
+      bool interior = (n0 + BN <= p.N) && (!p.causal || m0 + p_seq >= n0 + BN - 1);
+      if (p.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
+      if (p.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
+      int cmin = 0, cmax = 32;
+      if (p.causal) cmin = max(cmin, key - p_seq - m0 - cg * 32);
+      if (p.mode) {
+        const int cnear = p.w + key - p_seq - m0 - cg * 32;  // columns below it are near pairs
+        if (p.mode == 1) cmax = min(cmax, cnear);
+        else cmin = max(cmin, cnear);
+      }
+      if (!key_ok) cmin = 32;
+      const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
+
+      bool w_ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
+      if (w_ok && drain) w_ok = mbar_wait(bar(FB_DQ_FULL), (t - 1) & 1, actx, 915);
+      w_ok = __all_sync(0xffffffffu, w_ok);
+      if (!w_ok) return false;
+      tc_fence_after();
+      uint32_t sr[32];
+      tmem_ld32(tlane + C::kColS + cg * 32, sr);
+      tmem_wait_ld();
+      uint32_t pk[16];
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t qr[QQ];
+        if (drain) {
+          if (QQ == 8) tmem_ld8(tlane + C::kColB + cg * QC + qd * QQ, qr);
+          else tmem_ld4(tlane + C::kColB + cg * QC + qd * QQ, qr);
+        }
+#pragma unroll
+        for (int c = 8 * qd; c < 8 * qd + 8; ++c) {
+          const float lc = __shfl_sync(0xffffffffu, lse_lane, c);
+          pv[c] = fmaf(__uint_as_float(sr[c]), qk_scale, -lc);
+          if (!interior) pv[c] = ((unsigned)(c - cmin) < cwidth) ? pv[c] : -INFINITY;  // exp2 -> 0
+        }
+#pragma unroll
+        for (int c = 8 * qd; c < 8 * qd + 8; c += 2) {
+          pv[c] = ex2(pv[c]);
+          pv[c + 1] = ex2(pv[c + 1]);
+          pk[c >> 1] = TcElem<T>::pack(pv[c], pv[c + 1]);
+        }
+        if (drain) {
+          tmem_wait_ld();
+          if (qd == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(FB_DQ_FREE));   // dP^T of this tile may overwrite dQ
+          }
+          if (dq_dst) {
+#pragma unroll
+            for (int j = 0; j < QQ / 4; ++j)
+              red_add_v4(dq_dst + (int64_t)(qd * (QQ / 4) + j) * fp.Mpad * 4, qr[4 * j], qr[4 * j + 1],
+                         qr[4 * j + 2], qr[4 * j + 3]);
+          }
+        }
+      }
+      tmem_st16(tlane + C::kColS + cg * 32, pk);  // inside this thread's own columns
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FB_P1));
+      return true;
+    };
+
+    if (T_tiles > 0) ok = phase1(0, false, nullptr);
+    for (int t = 0; t < T_tiles && ok; ++t) {
+      // ---- phase 2: dS^T = P^T * (dP^T - delta) into shared memory ----
+      ok = mbar_wait(bar(FB_DP_FULL), t & 1, actx, 913);
+      if (ok && t > 0) ok = mbar_wait(bar(FB_DS_FREE), (t - 1) & 1, actx, 914);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        uint32_t sr[32];
+        tmem_ld32(tlane + C::kColB + cg * 32, sr);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float d0 = __shfl_sync(0xffffffffu, dlt_lane, c);
+          const float d1 = __shfl_sync(0xffffffffu, dlt_lane, c + 1);
+          pk[c >> 1] = TcElem<T>::pack(pv[c] * (__uint_as_float(sr[c]) - d0),
+                                       pv[c + 1] * (__uint_as_float(sr[c + 1]) - d1));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4 *>(ds_row + (((ds_chunk0 + j) ^ ds_xor) << 4)) =
+              make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+      }
+      fence_proxy_async_smem();   // the MMAs read dS^T through the async proxy
+      tc_fence_before();          // and dQ(t) overwrites the dP^T columns just read
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FB_P2));
+
+      // ---- phase 1 of the next tile, with the read-out of dQ(t) woven in ----
+      // dQ rows are queries: this thread owns row `row` of the tile and QC of its columns
+      const int m_t = t_cur.mt * BM + row;
+      float *dq_dst = nullptr;
+      if (m_t < p.M)
+        dq_dst = fp.dq_acc +
+                 (((int64_t)b * p.H + t_cur.h) * (D / 4) + cg * (QC / 4)) * (int64_t)fp.Mpad * 4 +
+                 (int64_t)m_t * 4;
+      advance(t_cur);
+      if (t + 1 < T_tiles) {
+        ok = phase1(t + 1, true, dq_dst);
+        if (!ok) break;
+      } else {
+        // last tile: plain read-out
+        ok = mbar_wait(bar(FB_DQ_FULL), t & 1, actx, 917);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t qr[QC];
+        if (QC == 32) tmem_ld32(tlane + C::kColB + cg * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
+        else tmem_ld16(tlane + C::kColB + cg * QC, qr);
+        tmem_wait_ld();
+        if (dq_dst) {
+#pragma unroll
+          for (int j = 0; j < QC / 4; ++j)
+            red_add_v4(dq_dst + (int64_t)j * fp.Mpad * 4, qr[4 * j], qr[4 * j + 1], qr[4 * j + 2],
+                       qr[4 * j + 3]);
+        }
+      }
+    }
+
+    if (ok && T_tiles > 0) {
+      ok = mbar_wait(bar(FB_DONE), 0, actx, 916);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      // warps of column groups 0 / 1 store dK, groups 2 / 3 store dV; each thread half a row
+      const int which = cg >> 1, half = cg & 1;
+      constexpr int COLS = D / 2;
+      T *orow = which == 0 ? row_ptr_mut<T>(p.dk, p.sdk, b, hk, key)
+                           : row_ptr_mut<T>(p.dv, p.sdv, b, hk, key);
+      const float scale = which == 0 ? p.sm_scale : 1.f;
+      const uint32_t col_base = which == 0 ? C::kColDK : C::kColDV;
+#pragma unroll
+      for (int c = 0; c < COLS / 32; ++c) {
+        uint32_t ov[32];
+        const int col0 = half * COLS + c * 32;
+        if (T_tiles > 0) {
+          tmem_ld32(tlane + col_base + col0, ov);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (which == 1 && p.dv_accumulate && key_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 old = *reinterpret_cast<const uint4 *>(orow + col0 + i * 8);
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const float2 f = TcElem<T>::unpack(ow[e2]);
+              ov[8 * i + 2 * e2] = __float_as_uint(__uint_as_float(ov[8 * i + 2 * e2]) + f.x);
+              ov[8 * i + 2 * e2 + 1] = __float_as_uint(__uint_as_float(ov[8 * i + 2 * e2 + 1]) + f.y);
+            }
+          }
+        }
+        if (key_ok) store_row32<T>(orow + col0, ov, scale);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+// dq = dq_acc * scale, converted to 16 bits.  Block = 32 queries x 8 warps; warp w converts the
+// eight-column groups w, w + 8, ... of its 32 rows (lane = row: the fp32 reads are 512-byte runs).
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+    dq_convert_kernel(const float *__restrict__ acc, void *dq, Strides sdq, int H, int M, int Mpad,
+                      float scale) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int m = blockIdx.x * 32 + lane;
+  const int h = blockIdx.y, b = blockIdx.z;
+  if (m >= M) return;
+  const float *src = acc + ((int64_t)b * H + h) * (D / 4) * (int64_t)Mpad * 4 + (int64_t)m * 4;
+  T *orow = row_ptr_mut<T>(dq, sdq, b, h, m);
+#pragma unroll
+  for (int g = w; g < D / 8; g += 8) {
+    const float4 lo = *reinterpret_cast<const float4 *>(src + (int64_t)(2 * g) * Mpad * 4);
+    const float4 hi = *reinterpret_cast<const float4 *>(src + (int64_t)(2 * g + 1) * Mpad * 4);
+    uint4 v;
+    v.x = TcElem<T>::pack(lo.x * scale, lo.y * scale);
+    v.y = TcElem<T>::pack(lo.z * scale, lo.w * scale);
+    v.z = TcElem<T>::pack(hi.x * scale, hi.y * scale);
+    v.w = TcElem<T>::pack(hi.z * scale, hi.w * scale);
+    *reinterpret_cast<uint4 *>(orow + g * 8) = v;
+  }
+}
+
+}  // namespace tc
+}  // namespace fa

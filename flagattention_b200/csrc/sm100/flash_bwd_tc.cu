@@ -67,7 +67,7 @@ static int launch_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, const fa_te
   p.dv_accumulate = dv_accumulate;
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
   dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
-  kern<<<grid, kBwdThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
+  kern<<<grid, kDkdvThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
   FA_CHECK_LAUNCH();
   return FA_OK;
 }

@@ -71,17 +71,23 @@ struct DkdvTcCfg {
   static constexpr int kQ0 = 2 * kTile;                // Q ring: NQ x (Q tile)
   static constexpr int kDO0 = kQ0 + NQ * kTile;        // dO ring: NDO x (dO tile)
   static constexpr int kBars = kDO0 + NDO * kTile;
-  static constexpr int kMisc = kBars + 24 * 8;
+  static constexpr int kStats = kBars + 24 * 8;        // lse[128] | delta[128] of the current tile
+  static constexpr int kMisc = kStats + 2 * 128 * 4;
   static constexpr int kTotal = kMisc + 16 + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + D;
+  static_assert(kTotal <= 232448, "shared memory budget");
 };
 
 enum DkdvBar { KV_KV_FULL = 0, KV_Q_FULL = 1, KV_Q_FREE = 4, KV_DO_FULL = 7, KV_DO_FREE = 9,
-               KV_S_FULL = 11, KV_DP_FULL = 12, KV_P1 = 13, KV_P2 = 14, KV_DONE = 15 };
+               KV_S_FULL = 11, KV_DP_FULL = 12, KV_P1 = 13, KV_P2 = 14, KV_DONE = 15,
+               KV_LSE_FULL = 16, KV_DLT_FULL = 17 };
+
+// the dK/dV kernel has one more warp, which stages lse / delta of every tile in shared memory
+constexpr int kDkdvThreads = kBwdThreads + 32;
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDkdvThreads, 1)
     flash_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                              const __grid_constant__ CUtensorMap map_do,
                              const __grid_constant__ CUtensorMap map_k,
@@ -133,6 +139,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     mbar_init(bar(KV_P1), kEwWarps);
     mbar_init(bar(KV_P2), kEwWarps);
     mbar_init(bar(KV_DONE), 1);
+    mbar_init(bar(KV_LSE_FULL), 1);
+    mbar_init(bar(KV_DLT_FULL), 1);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -269,6 +277,39 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         mbar_wait(bar(KV_DONE), 0, actx, 806);
       }
     }
+  } else if (warp == 2 + kEwWarps) {
+    // ------------------------------ statistics warp ----------------------------
+    // lse (in the base-2 domain) and delta of the 128 queries of every tile go through shared
+    // memory, where the element-wise threads read them as broadcast vectors: every thread needs
+    // the values of all its 32 query columns.  Queries past M get lse = +inf, which makes their P
+    // exactly zero.  One buffer each: lse(t) may be written once phase 1 of tile t - 1 is over,
+    // delta(t) once phase 2 of tile t - 1 is.
+    float4 *lse_s = reinterpret_cast<float4 *>(smem_gen + C::kStats);
+    float4 *dlt_s = lse_s + 32;
+    bool ok = true;
+    for (int t = 0; t < T_tiles; ++t) {
+      const int h = hk * G + t / tiles, m0 = (mt_lo + t % tiles) * BM;
+      const int m = m0 + lane * 4;
+      const int64_t li = ((int64_t)b * p.H + h) * p.M + m;
+      float l[4], d[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        l[j] = m + j < p.M ? p.lse[li + j] * kLog2e : INFINITY;
+        d[j] = m + j < p.M ? p.delta[li + j] : 0.f;
+      }
+      if (t > 0) ok = mbar_wait(bar(KV_P1), (t - 1) & 1, actx, 951);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      lse_s[lane] = make_float4(l[0], l[1], l[2], l[3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KV_LSE_FULL));
+      if (t > 0) ok = mbar_wait(bar(KV_P2), (t - 1) & 1, actx, 952);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      dlt_s[lane] = make_float4(d[0], d[1], d[2], d[3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KV_DLT_FULL));
+    }
   } else {
     // ------------------------------ element-wise warps --------------------------
     const int ew = warp - 2;
@@ -277,17 +318,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
     const float qk_scale = p.sm_scale * kLog2e;
     const bool key_ok = key < p.N;
+    // lse / delta of this thread's 32 query columns, as staged by the statistics warp
+    const float4 *lse_s = reinterpret_cast<const float4 *>(smem_gen + C::kStats) + cg * 8;
+    const float4 *dlt_s = lse_s + 32;
     bool ok = true;
 
     for (int t = 0; t < T_tiles; ++t) {
-      const int h = hk * G + t / tiles, m0 = (mt_lo + t % tiles) * BM;
-      // lane c of the warp fetches lse / delta of query column c of this thread's 32 columns;
-      // the loops below broadcast them with shuffles.  Queries past M get lse = +inf, which
-      // makes their P exactly zero.
-      const int qm_lane = m0 + cg * 32 + lane;
-      const int64_t li = ((int64_t)b * p.H + h) * p.M + qm_lane;
-      const float lse_lane = qm_lane < p.M ? p.lse[li] * kLog2e : INFINITY;
-      const float dlt_lane = qm_lane < p.M ? p.delta[li] : 0.f;
+      const int m0 = (mt_lo + t % tiles) * BM;
       // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
       // masking at all; the others mask with one unsigned range check per element:
       // column c is visible iff cmin <= c < cmin + cwidth.
@@ -305,7 +342,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
 
       // ---- phase 1: P^T = exp2(S^T * scale - lse), written over S^T ----
-      ok = mbar_wait(bar(KV_S_FULL), t & 1, actx, 901);
+      ok = mbar_wait(bar(KV_LSE_FULL), t & 1, actx, 900);
+      if (ok) ok = mbar_wait(bar(KV_S_FULL), t & 1, actx, 901);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -315,9 +353,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       float pv[32];
       uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float lc = __shfl_sync(0xffffffffu, lse_lane, c);
-        pv[c] = fmaf(__uint_as_float(sr[c]), qk_scale, -lc);
+      for (int i = 0; i < 8; ++i) {
+        const float4 l4 = lse_s[i];
+        pv[4 * i + 0] = fmaf(__uint_as_float(sr[4 * i + 0]), qk_scale, -l4.x);
+        pv[4 * i + 1] = fmaf(__uint_as_float(sr[4 * i + 1]), qk_scale, -l4.y);
+        pv[4 * i + 2] = fmaf(__uint_as_float(sr[4 * i + 2]), qk_scale, -l4.z);
+        pv[4 * i + 3] = fmaf(__uint_as_float(sr[4 * i + 3]), qk_scale, -l4.w);
       }
       if (!interior) {
 #pragma unroll
@@ -337,18 +378,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       if (lane == 0) mbar_arrive(bar(KV_P1));
 
       // ---- phase 2: dS^T = P^T * (dP^T - delta), written over dP^T ----
-      ok = mbar_wait(bar(KV_DP_FULL), t & 1, actx, 903);
+      ok = mbar_wait(bar(KV_DLT_FULL), t & 1, actx, 902);
+      if (ok) ok = mbar_wait(bar(KV_DP_FULL), t & 1, actx, 903);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       tmem_ld32(tlane + C::kColDP + cg * 32, sr);
       tmem_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const float d0 = __shfl_sync(0xffffffffu, dlt_lane, c);
-        const float d1 = __shfl_sync(0xffffffffu, dlt_lane, c + 1);
-        pk[c >> 1] = TcElem<T>::pack(pv[c] * (__uint_as_float(sr[c]) - d0),
-                                     pv[c + 1] * (__uint_as_float(sr[c + 1]) - d1));
+      for (int i = 0; i < 8; ++i) {
+        const float4 d4 = dlt_s[i];
+        pk[2 * i] = TcElem<T>::pack(pv[4 * i] * (__uint_as_float(sr[4 * i]) - d4.x),
+                                    pv[4 * i + 1] * (__uint_as_float(sr[4 * i + 1]) - d4.y));
+        pk[2 * i + 1] = TcElem<T>::pack(pv[4 * i + 2] * (__uint_as_float(sr[4 * i + 2]) - d4.z),
+                                        pv[4 * i + 3] * (__uint_as_float(sr[4 * i + 3]) - d4.w));
       }
       tmem_st16(tlane + C::kColDP + cg * 32, pk);
       tmem_wait_st();

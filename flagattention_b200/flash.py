@@ -6,6 +6,7 @@ when any return_* flag is set), same AssertionErrors on bad shapes, autograd
 through q, k, v only.  The kernels run on the current CUDA stream of the
 inputs' device.
 """
+import ctypes
 import math
 
 import torch
@@ -81,6 +82,18 @@ def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None, dropout_p=0.0, see
         _C.check(st, "fa_flash_bwd_delta")
         if mark:
             mark("delta")
+        ws_bytes = lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+        if ws_bytes > 0:
+            # one pass over the score tiles; dq is accumulated in an fp32 workspace
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+            st = lib.fa_flash_bwd_fused(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
+                                        _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdq),
+                                        _C.byref(tdk), _C.byref(tdv), _C.fptr(ws),
+                                        ctypes.c_int64(ws_bytes), stream)
+            _C.check(st, "fa_flash_bwd_fused")
+            if mark:
+                mark("dkdvdq")
+            return dq, dk, dv
         st = lib.fa_flash_bwd_dkdv(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
                                    _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdk),
                                    _C.byref(tdv), stream)

@@ -122,6 +122,22 @@ int fa_flash_bwd_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tenso
                     const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                     const float *delta, const fa_tensor4 *dq, void *stream);
 
+/* dk, dv (Hk heads) and dq from ONE pass over the score tiles (head_dim 64 / 128 on the
+ * tensor-core path): S and dP are computed once instead of once per kernel.  Replaces the pair
+ * of launches `_bwd_kv_kernel` + `_bwd_q_kernel` (src/flag_attn/flash.py:204-249).  dq is
+ * accumulated with fp32 global reductions in `workspace`, so it is reproducible to fp32
+ * rounding only (dk, dv are bitwise reproducible).
+ * fa_flash_bwd_fused_workspace_bytes returns the bytes of device memory `workspace` must hold
+ * (16-byte aligned), or 0 when the shape is not covered: then call fa_flash_bwd_dkdv and
+ * fa_flash_bwd_dq.  fa_flash_bwd_fused on an uncovered shape returns FA_ERR_UNSUPPORTED, with a
+ * missing / short workspace FA_ERR_WORKSPACE. */
+int64_t fa_flash_bwd_fused_workspace_bytes(const fa_flash_shape *s);
+int fa_flash_bwd_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                       const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                       const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
+                       const fa_tensor4 *dv, void *workspace, int64_t workspace_bytes,
+                       void *stream);
+
 /* Regenerates the dropout keep-mask of a flash_attention call: mask[b,h,m,n] (1 byte each,
  * contiguous) = 1 iff the element was kept.  Replaces `recompute_mask_kernel`
  * (src/flag_attn/testing/dropout.py:5-25). */

@@ -132,8 +132,9 @@ def test_empty_rows_give_zero_output_and_neg_inf_lse():
     assert torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
 
 
-def test_deterministic_and_stream_safe():
-    """No atomics anywhere: two runs are bitwise identical; a side stream gives the same bits."""
+def _three_runs(monkeypatch, two_kernels):
+    if two_kernels:
+        monkeypatch.setenv("FLAGATTN_B200_BWD_TWO_KERNELS", "1")
     q, k, v, do = make_qkv(2, 4, 2, 777, 901, 128, torch.bfloat16, "cuda", seed=11)
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
     outs = []
@@ -145,9 +146,42 @@ def test_deterministic_and_stream_safe():
             g = torch.autograd.grad(o, (q, k, v), do)
         stream.synchronize()
         outs.append((o, *g))
+    return outs
+
+
+def test_deterministic_and_stream_safe(monkeypatch):
+    """Two runs, and a run on a side stream, give the same bits for o, dk, dv.  dq of the one-pass
+    backward is a sum of fp32 reductions in arbitrary order: equal to within a 16-bit rounding step."""
+    outs = _three_runs(monkeypatch, two_kernels=False)
+    for other in outs[1:]:
+        for i, (a, b) in enumerate(zip(outs[0], other)):
+            if i == 1:   # dq
+                assert (a.float() - b.float()).abs().max().item() <= 2 ** -7 * a.float().abs().max().item()
+            else:
+                assert torch.equal(a, b)
+
+
+def test_two_kernel_backward_is_bitwise_deterministic(monkeypatch):
+    """The dK/dV + dQ kernel pair uses no atomics: every output is bitwise reproducible."""
+    outs = _three_runs(monkeypatch, two_kernels=True)
     for other in outs[1:]:
         for a, b in zip(outs[0], other):
             assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal", [(1, 4, 4, 1024, 1024, 128, True), (2, 4, 2, 500, 700, 64, True),
+                                                  (1, 2, 2, 333, 1111, 128, False), (1, 2, 1, 1500, 300, 64, True)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_one_pass_backward_matches_two_kernel_backward(monkeypatch, B, Hq, Hk, M, N, D, causal, dtype):
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", seed=5 + M)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = fa.flash_attention(q, k, v, causal)
+    g1 = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+    monkeypatch.setenv("FLAGATTN_B200_BWD_TWO_KERNELS", "1")
+    g2 = torch.autograd.grad(o, (q, k, v), do)
+    for a, b in zip(g1, g2):
+        scale = b.float().abs().max().item()
+        assert (a.float() - b.float()).abs().max().item() <= 2 ** -6 * scale + 1e-6
 
 
 def test_golden_fixtures_on_gpu():

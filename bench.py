@@ -241,23 +241,27 @@ def run_flash(args, dist, rank, world, device):
     e2e_steps = max(2, min(args.steps, 5))
     outs_host = [torch.empty((B, H, L, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
 
-    # The step is pipelined over the batch dimension on two streams, so that the host-to-device
-    # copy of one batch element overlaps the kernels and the device-to-host copy of the previous one.
-    streams = [torch.cuda.Stream(device=device) for _ in range(2)]
+    # The step is pipelined over (batch element, group of 8 heads) chunks on three streams, so that
+    # the host-to-device copy of one chunk overlaps the kernels of another and the device-to-host
+    # copy of a third: both PCIe directions stay busy and the fill / drain of the pipeline is one
+    # chunk (1/16 of the step), not one batch element.
+    streams = [torch.cuda.Stream(device=device) for _ in range(3)]
+    HG = 8 if H % 8 == 0 else H
+    chunks = [(bi, h0) for bi in range(B) for h0 in range(0, H, HG)]
 
     def e2e_step():
         cur = torch.cuda.current_stream(device)
         for st in streams:
             st.wait_stream(cur)
-        for bi in range(B):
-            st = streams[bi % 2]
+        for ci, (bi, h0) in enumerate(chunks):
+            st = streams[ci % len(streams)]
             with torch.cuda.stream(st):
-                qd, kd, vd, dod = (t[bi:bi + 1].to(device, non_blocking=True) for t in host)
+                qd, kd, vd, dod = (t[bi:bi + 1, h0:h0 + HG].to(device, non_blocking=True) for t in host)
                 qd.requires_grad_(), kd.requires_grad_(), vd.requires_grad_()
                 o = fa.flash_attention(qd, kd, vd, causal=True)
                 grads = torch.autograd.grad(o, (qd, kd, vd), dod)
                 for dst, src in zip(outs_host, (o.detach(), *grads)):
-                    dst[bi:bi + 1].copy_(src, non_blocking=True)
+                    dst[bi:bi + 1, h0:h0 + HG].copy_(src, non_blocking=True)
         for st in streams:
             cur.wait_stream(st)
 

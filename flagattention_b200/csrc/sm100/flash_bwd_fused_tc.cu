@@ -56,7 +56,7 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
   if (cudaMemsetAsync(workspace, 0, (size_t)fused_workspace_bytes(s), stream) != cudaSuccess)
     return FA_ERR_LAUNCH;
   dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
-  kern<<<grid, kBwdThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, fp);
+  kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, fp);
   FA_CHECK_LAUNCH();
   dim3 cgrid((s->M + 31) / 32, s->H, s->B);
   dq_convert_kernel<T, D><<<cgrid, 256, 0, stream>>>(workspace, dq->ptr, strides_of(dq), s->H,

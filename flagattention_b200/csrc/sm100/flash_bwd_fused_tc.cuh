@@ -4,24 +4,27 @@
 //
 // One CTA per 128 keys walks the query tiles (and the query heads of its GQA group).  dK and dV
 // accumulate in TMEM for the whole walk.  The dQ contribution of a tile, dS K, is a complete
-// 128 x D product of its own: it is accumulated in TMEM for the tile, read back by the
-// element-wise warps and added into an fp32 workspace in global memory with vector reductions
-// (`red.global.add.v4.f32`); a small kernel scales and converts the workspace afterwards.  The
+// 128 x D product of its own: it is accumulated in TMEM for the tile, read back by four
+// reduction warps and added into an fp32 workspace in global memory with vector reductions
+// (`cp.reduce.async.bulk`); a small kernel scales and converts the workspace afterwards.  The
 // order of those additions is not fixed, so dQ is reproducible only to fp32 rounding.
 //
 //   warp 0       TMA producer
 //   warp 1       MMA issuer (one thread); every MMA is 128 x 128 x 16 (128 x 64 x 16 at D = 64)
 //   warps 2..17  element-wise stage, one thread per (accumulator row, 32 columns)
+//   warps 18..21 dQ reduction: TMEM -> shared-memory staging -> cp.reduce.async.bulk
 //
-// TMEM (512 columns):  S^T / P^T | dP^T, then dQ | dK | dV.
-// Shared memory:       K, V resident | Q ring | dO ring | dS^T (16-bit, 128-byte swizzle).
-// dS^T is written once to shared memory and read by two GEMMs under two descriptors: as the
-// K-major A operand of dK += dS^T Q and as the MN-major A operand of dQ = dS K.
+// TMEM (512 columns):  S^T, then dP^T | dQ | dK | dV.
+//   The two score products of a tile share one 128-column region: dP^T is issued as soon as the
+//   element-wise warps hold S^T in registers, S^T of the next tile as soon as they hold dP^T.
+//   dQ has columns of its own, so its slow read-out never holds a GEMM back.
+// Shared memory:       K, V resident | Q ring | dO ring | one 16-bit 128 x 128 tile "PD" | dQ staging.
+//   PD holds P^T (A operand of dV += P^T dO), then dS^T of the same tile: the K-major A operand of
+//   dK += dS^T Q and, under a second descriptor, the MN-major A operand of dQ = dS K.
 //
-// Issue order of a tile (tensor pipe, in order):   dV(t) | S^T(t+1) | dQ(t) | dK(t) | dP^T(t+1)
-// Element-wise order:                              phase 2 (t) | phase 1 (t+1) with the dQ(t) read-out woven in
-//   phase 1: P^T = exp2(S^T * scale - L), written over S^T (TMEM A operand of dV += P^T dO)
-//   phase 2: dS^T = P^T * (dP^T - delta), written to shared memory
+// Issue order of a tile (tensor pipe, in order):   dP^T(t) | dV(t) | S^T(t+1) | dQ(t) | dK(t)
+// Element-wise order:                              phase 1 (t) | phase 2 (t)
+//   phase 1: P^T = exp2(S^T * scale - L) -> PD       phase 2: dS^T = P^T * (dP^T - delta) -> PD
 #pragma once
 
 #include "flash_bwd_tc.cuh"
@@ -31,42 +34,78 @@ namespace tc {
 
 template <int D>
 struct FusedBwdCfg {
-  static constexpr int BM = 128, BN = 128, NQ = 3, NDO = (D == 128 ? 1 : 2);
+  static constexpr int BM = 128, BN = 128, NQ = 2, NDO = (D == 128 ? 1 : 2);
   static constexpr int KSUB = D / 64;
   static constexpr int kTile = 128 * D * 2;            // any 128-row operand tile
   static constexpr int kK = 0;
   static constexpr int kV = kTile;
   static constexpr int kQ0 = 2 * kTile;                // Q ring
   static constexpr int kDO0 = kQ0 + NQ * kTile;        // dO ring
-  static constexpr int kDS = kDO0 + NDO * kTile;       // dS^T: 128 key rows x 128 queries x 2 B
-  static constexpr int kDsBytes = 128 * 128 * 2;
-  static constexpr int kBars = kDS + kDsBytes;
+  static constexpr int kPD = kDO0 + NDO * kTile;       // P^T / dS^T: 128 key rows x 128 queries x 2 B
+  static constexpr int kPdBytes = 128 * 128 * 2;
+  // dQ staging: two buffers of a quarter of a dQ tile, fp32, as D/16 runs of (128 queries x 4)
+  static constexpr int kQuarter = (D / 16) * 2048;
+  static constexpr int kStage = kPD + kPdBytes;
+  static constexpr int kBars = kStage + 2 * kQuarter;
   static constexpr int kMisc = kBars + 24 * 8;
   static constexpr int kTotal = kMisc + 16 + 1024;
   static constexpr int kTmemCols = 512;
-  static constexpr int kColS = 0, kColB = 128, kColDK = 256, kColDV = 256 + D;
+  static constexpr int kColA = 0, kColQ = 128, kColDK = 256, kColDV = 256 + D;
   static_assert(kTotal <= 232448, "shared memory budget");
 };
 
-enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 4, FB_DO_FULL = 7, FB_DO_FREE = 9,
-                FB_S_FULL = 11, FB_DP_FULL = 12, FB_P1 = 13, FB_P2 = 14, FB_DQ_FULL = 15,
-                FB_DQ_FREE = 16, FB_DS_FREE = 17, FB_DONE = 18 };
+enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB_DO_FREE = 7,
+                FB_S_FULL = 9, FB_S_LOADED = 10, FB_DP_FULL = 11, FB_DP_LOADED = 12,
+                FB_PT_FULL = 13, FB_PT_FREE = 14, FB_DS_FULL = 15, FB_DS_FREE = 16,
+                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19 };
 
 struct FusedBwdParams {
   BwdTcParams base;
-  float *dq_acc;   // (B, H, D / 4, Mpad, 4) fp32, zeroed before the launch
+  float *dq_acc;   // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
   int Mpad;        // M rounded up to a multiple of 128
 };
 
-__device__ __forceinline__ void red_add_v4(float *dst, uint32_t a, uint32_t b, uint32_t c,
-                                           uint32_t d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst), "f"(__uint_as_float(a)),
-               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+// fp32 add of `bytes` contiguous bytes of shared memory into global memory, done by the copy
+// engine: it does not pass through the load/store queue of the SM and nobody waits for it.
+__device__ __forceinline__ void bulk_reduce_add_f32(float *dst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;\n" ::"l"(dst),
+               "r"(smem_src), "r"(bytes)
                : "memory");
 }
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+}
+// waits until all but the newest group have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read_1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+}
+// barrier among the four reduction warps (barrier 0 belongs to __syncthreads)
+__device__ __forceinline__ void red_warps_sync() {
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
+}
+// the same barrier with a vote: true iff `ok` holds in all 128 threads
+__device__ __forceinline__ bool red_warps_all(bool ok) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}\n"
+      : "=r"(out)
+      : "r"((uint32_t)ok)
+      : "memory");
+  return out != 0;
+}
+
+// warps: 0 TMA producer, 1 MMA issuer, 2..17 element-wise, 18..21 dQ reduction (one per TMEM
+// lane slice)
+constexpr int kFusedThreads = kBwdThreads + 4 * 32;   // 704
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kFusedThreads, 1)
     flash_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                               const __grid_constant__ CUtensorMap map_do,
                               const __grid_constant__ CUtensorMap map_k,
@@ -115,12 +154,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       mbar_init(bar(FB_DO_FREE + s), 1);
     }
     mbar_init(bar(FB_S_FULL), 1);
+    mbar_init(bar(FB_S_LOADED), kEwWarps);
     mbar_init(bar(FB_DP_FULL), 1);
-    mbar_init(bar(FB_P1), kEwWarps);
-    mbar_init(bar(FB_P2), kEwWarps);
-    mbar_init(bar(FB_DQ_FULL), 1);
-    mbar_init(bar(FB_DQ_FREE), kEwWarps);
+    mbar_init(bar(FB_DP_LOADED), kEwWarps);
+    mbar_init(bar(FB_PT_FULL), kEwWarps);
+    mbar_init(bar(FB_PT_FREE), 1);
+    mbar_init(bar(FB_DS_FULL), kEwWarps);
     mbar_init(bar(FB_DS_FREE), 1);
+    mbar_init(bar(FB_DQ_FULL), 1);
+    mbar_init(bar(FB_DQ_FREE), 4);
     mbar_init(bar(FB_DONE), 1);
     fence_barrier_init();
   }
@@ -148,8 +190,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       int issued_q = 0, issued_do = 0;
       bool ok = true;
       int sq = 0, phq = 1, sd = 0, phd = 1;   // slot and the "free" parity to wait for
+      int h = hk * G, mt = mt_lo;
       for (int t = 0; t < T_tiles; ++t) {
-        const int h = hk * G + t / tiles, m0 = (mt_lo + t % tiles) * BM;
+        const int m0 = mt * BM;
         ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 711);
         if (!ok) break;
         mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
@@ -166,6 +209,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         ++issued_do;
         if (++sq == NQ) sq = 0, phq ^= 1;
         if (++sd == NDO) sd = 0, phd ^= 1;
+        if (++mt == mt_hi) mt = mt_lo, ++h;
       }
       if (!ok) {
         // let copies already in flight land before the CTA gives its shared memory back
@@ -189,9 +233,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const uint32_t q_mn_lo = smem_desc_lo(smem + C::kQ0, BM * 128);     // Q as MN-major B operand
       const uint32_t do_k_lo = smem_desc_lo(smem + C::kDO0, 0);
       const uint32_t do_mn_lo = smem_desc_lo(smem + C::kDO0, BM * 128);
-      const uint32_t ds_k_lo = smem_desc_lo(smem + C::kDS, 0);            // dS^T as K-major A of dK
-      const uint32_t ds_mn_lo = smem_desc_lo(smem + C::kDS, BN * 128);    // dS as MN-major A of dQ
+      const uint32_t pd_k_lo = smem_desc_lo(smem + C::kPD, 0);            // P^T / dS^T, K-major A
+      const uint32_t pd_mn_lo = smem_desc_lo(smem + C::kPD, BN * 128);    // dS, MN-major A of dQ
       bool ok = mbar_wait(bar(FB_KV_FULL), 0, actx, 811);
+      // S^T = K Q^T into the score columns
       auto issue_s = [&](int sq, int phq) -> bool {
         if (!mbar_wait(bar(FB_Q_FULL + sq), phq, actx, 812)) return false;
         tc_fence_after();
@@ -199,54 +244,64 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
-          mma_ss_lo(tmem + C::kColS, k_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
+          mma_ss_lo(tmem + C::kColA, k_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
         }
         mma_commit(bar(FB_S_FULL));
         return true;
       };
-      auto issue_dp = [&](int sd, int phd) -> bool {
-        if (!mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 813)) return false;
-        tc_fence_after();
-        const uint32_t b_lo = do_k_lo + sd * kTile16;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
-          mma_ss_lo(tmem + C::kColB, v_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
-        }
-        mma_commit(bar(FB_DP_FULL));
-        return true;
-      };
       if (ok) ok = issue_s(0, 0);
-      if (ok) ok = issue_dp(0, 0);
       int sq = 0, phq = 0, sd = 0, phd = 0;
       for (int t = 0; t < T_tiles && ok; ++t) {
-        int nsq = sq + 1, nphq = phq, nsd = sd + 1, nphd = phd;
+        int nsq = sq + 1, nphq = phq;
         if (nsq == NQ) nsq = 0, nphq ^= 1;
-        if (nsd == NDO) nsd = 0, nphd ^= 1;
         const uint32_t acc = t > 0 ? 1u : 0u;
         const uint32_t par = t & 1;
-        // dV += P^T(t) dO(t)
-        ok = mbar_wait(bar(FB_P1), par, actx, 814);
+        // dP^T(t) = V dO^T over S^T(t), once every element-wise warp holds S^T(t) in registers
+        ok = mbar_wait(bar(FB_S_LOADED), par, actx, 813);
+        if (ok) ok = mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 814);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const uint32_t b_lo = do_k_lo + sd * kTile16;
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
+            mma_ss_lo(tmem + C::kColA, v_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
+          }
+          mma_commit(bar(FB_DP_FULL));
+        }
+        // dV += P^T(t) dO(t), P^T from shared memory
+        ok = mbar_wait(bar(FB_PT_FULL), par, actx, 815);
         if (!ok) break;
         tc_fence_after();
         {
           const uint32_t b_lo = do_mn_lo + sd * kTile16;
 #pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk)
-            mma_ts_lo(tmem + C::kColDV, tmem + C::kColS + (kk >> 1) * 32 + (kk & 1) * 8,
-                      b_lo + ((kk * 16 * 128) >> 4), idesc_acc, kk > 0 ? 1u : acc);
+          for (int kk = 0; kk < BM / 16; ++kk) {
+            const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
+            mma_ss_lo(tmem + C::kColDV, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
+                      kk > 0 ? 1u : acc);
+          }
           mma_commit(bar(FB_DO_FREE + sd));
+          mma_commit(bar(FB_PT_FREE));
         }
-        if (t + 1 < T_tiles) ok = issue_s(nsq, nphq);
-        if (!ok) break;
-        ok = mbar_wait(bar(FB_P2), par, actx, 815);
+        // S^T(t+1), once every element-wise warp holds dP^T(t) in registers
+        if (t + 1 < T_tiles) {
+          ok = mbar_wait(bar(FB_DP_LOADED), par, actx, 816);
+          if (!ok) break;
+          tc_fence_after();
+          ok = issue_s(nsq, nphq);
+          if (!ok) break;
+        }
+        // dQ(t) = dS(t) K, a fresh accumulator: the read-out of dQ(t-1) must be over
+        ok = mbar_wait(bar(FB_DS_FULL), par, actx, 817);
+        if (ok && t > 0) ok = mbar_wait(bar(FB_DQ_FREE), (t - 1) & 1, actx, 818);
         if (!ok) break;
         tc_fence_after();
-        // dQ(t) = dS(t) K, a fresh accumulator over the dP^T columns
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint32_t off16 = (kk * 16 * 128) >> 4;
-          mma_ss_lo(tmem + C::kColB, ds_mn_lo + off16, k_mn_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
+          mma_ss_lo(tmem + C::kColQ, pd_mn_lo + off16, k_mn_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
         }
         mma_commit(bar(FB_DQ_FULL));
         // dK += dS^T(t) Q(t)
@@ -255,25 +310,77 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll
           for (int kk = 0; kk < BM / 16; ++kk) {
             const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
-            mma_ss_lo(tmem + C::kColDK, ds_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
+            mma_ss_lo(tmem + C::kColDK, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
                       kk > 0 ? 1u : acc);
           }
           mma_commit(bar(FB_Q_FREE + sq));
           mma_commit(bar(FB_DS_FREE));
         }
-        if (t + 1 < T_tiles) {
-          ok = mbar_wait(bar(FB_DQ_FREE), par, actx, 816);   // dQ(t) has been read out
-          if (!ok) break;
-          tc_fence_after();
-          ok = issue_dp(nsd, nphd);
-        }
-        sq = nsq, phq = nphq, sd = nsd, phd = nphd;
+        sq = nsq, phq = nphq;
+        if (++sd == NDO) sd = 0, phd ^= 1;
       }
       if (ok) {
         mma_commit(bar(FB_DONE));
-        mbar_wait(bar(FB_DONE), 0, actx, 817);
+        mbar_wait(bar(FB_DONE), 0, actx, 819);
       }
     }
+  } else if (warp >= 2 + kEwWarps) {
+    // ------------------------------ dQ reduction warps --------------------------
+    // dQ(t) = dS K is a complete 128 x D product per tile.  These four warps (one per TMEM lane
+    // slice = 32 query rows) move it out of TMEM a quarter of the columns at a time into a
+    // shared-memory staging buffer, from where the copy engine adds it to the fp32 workspace
+    // (`cp.reduce.async.bulk`, 2 KB runs).  An SM retires fp32 reductions at about 26 bytes per
+    // clock whoever issues them, so the 64 KB of a tile take about as long as its GEMMs; issued
+    // as `red` instructions they fill the load/store queue and stall every warp of the SM that
+    // shuffles or touches shared memory.  Two staging buffers: a quarter drains while the next
+    // is staged.
+    const int slice = warp & 3;
+    const int row = slice * 32 + lane;
+    const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
+    const bool issuer = (warp == 2 + kEwWarps) && lane == 0;
+    constexpr int QC = D / 4;                 // columns per quarter
+    int h = hk * G, mt = mt_lo;
+    int buf = 0;
+    bool ok = true;
+    for (int t = 0; t < T_tiles; ++t) {
+      // the tile's block of the workspace: D / 4 runs of (128 queries x 4 columns), contiguous
+      float *dst = fp.dq_acc + (((int64_t)b * p.H + h) * (fp.Mpad / BM) + mt) * (int64_t)(BM * D);
+      if (++mt == mt_hi) mt = mt_lo, ++h;
+      // every wait is bounded, so all four warps reach the vote; they leave together or not at all
+      ok = red_warps_all(mbar_wait(bar(FB_DQ_FULL), t & 1, actx, 921));
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t qr[QC];
+        if (QC == 32) tmem_ld32(tlane + C::kColQ + qd * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
+        else tmem_ld16(tlane + C::kColQ + qd * QC, qr);
+        tmem_wait_ld();
+        if (qd == 3) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(FB_DQ_FREE));   // dQ(t+1) may overwrite the columns
+        }
+        // the copy engine must have read what this buffer held two quarters ago
+        if (issuer) bulk_wait_read_1();
+        red_warps_sync();
+        uint8_t *stage = smem_gen + C::kStage + buf * C::kQuarter + row * 16;
+#pragma unroll
+        for (int g = 0; g < QC / 4; ++g)
+          *reinterpret_cast<uint4 *>(stage + g * 2048) =
+              make_uint4(qr[4 * g], qr[4 * g + 1], qr[4 * g + 2], qr[4 * g + 3]);
+        fence_proxy_async_smem();
+        red_warps_sync();
+        if (issuer) {
+          // one contiguous run per quarter; rows past M hold zeros and land in padding
+          bulk_reduce_add_f32(dst + qd * (C::kQuarter / 4), smem + C::kStage + buf * C::kQuarter,
+                              C::kQuarter);
+          bulk_commit();
+        }
+        buf ^= 1;
+      }
+    }
+    if (issuer) bulk_wait_all();   // shared memory must outlive the reads, the kernel the writes
   } else {
     // ------------------------------ element-wise warps --------------------------
     const int ew = warp - 2;
@@ -283,50 +390,44 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
     const float qk_scale = p.sm_scale * kLog2e;
     const bool key_ok = key < p.N;
-    // this thread's 64 bytes of a dS^T row: sub-tile cg / 2, 16-byte chunks (cg & 1) * 4 .. + 3
-    uint8_t *ds_row = smem_gen + C::kDS + (cg >> 1) * (128 * 128) + row * 128;
-    const int ds_chunk0 = (cg & 1) * 4, ds_xor = row & 7;
+    // this thread's 64 bytes of a PD row: sub-tile cg / 2, 16-byte chunks (cg & 1) * 4 .. + 3
+    uint8_t *pd_row = smem_gen + C::kPD + (cg >> 1) * (128 * 128) + row * 128;
+    const int pd_chunk0 = (cg & 1) * 4, pd_xor = row & 7;
+    auto store_pd = [&](const uint32_t (&pk)[16]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4 *>(pd_row + (((pd_chunk0 + j) ^ pd_xor) << 4)) =
+            make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    };
     bool ok = true;
 
-    float pv[32];
-    constexpr int QC = D / 4;   // dQ columns of this thread: 32 or 16
-    constexpr int QQ = QC / 4;  // per quarter of phase 1: 8 or 4
     // Lane c holds lse / delta of query column c of this thread's 32 columns (the loops below
     // broadcast them with shuffles); queries past M get lse = +inf, which makes their P exactly
     // zero.  The values of a tile are fetched one tile ahead, so their latency is off the
     // critical path.
-    float lse_next = INFINITY, dlt_next = 0.f, dlt_lane = 0.f;
-    // (head, query tile) of the tile whose statistics are fetched next, of the next phase 1 and
-    // of the tile in phase 2 / read-out: running counters, no divisions in the loop
-    struct TileIdx {
-      int h, mt;
-    };
-    TileIdx t_fetch{hk * G, mt_lo}, t_p1{hk * G, mt_lo}, t_cur{hk * G, mt_lo};
-    auto advance = [&](TileIdx &x) {
-      if (++x.mt == mt_hi) x.mt = mt_lo, ++x.h;
-    };
+    float lse_next = INFINITY, dlt_next = 0.f;
+    int h_f = hk * G, mt_f = mt_lo;   // tile whose statistics are fetched next
     auto fetch_stats = [&]() {
-      const int qm_lane = t_fetch.mt * BM + cg * 32 + lane;
-      const int64_t li = ((int64_t)b * p.H + t_fetch.h) * p.M + min(qm_lane, p.M - 1);
+      const int qm_lane = mt_f * BM + cg * 32 + lane;
+      const int64_t li = ((int64_t)b * p.H + h_f) * p.M + min(qm_lane, p.M - 1);
       // volatile: the loads must be issued here, a tile ahead of their use
       asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(lse_next) : "l"(p.lse + li));
       asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(dlt_next) : "l"(p.delta + li));
-      advance(t_fetch);
+      if (++mt_f == mt_hi) mt_f = mt_lo, ++h_f;
     };
     if (T_tiles > 0) fetch_stats();
-    // P^T(t) = exp2(S^T * scale - lse) into `pv` and, packed, over S^T in TMEM
-    // With `drain`, the dQ partial of the PREVIOUS tile is read out of TMEM on the way, a quarter
-    // after every quarter of the exponentials, and added to the fp32 workspace (dq_dst; null for
-    // rows past M).  The reductions leave the SM at a fixed rate (about one 32-byte sector per
-    // clock: 64 KB take as long as the GEMMs of a tile), so issued in one burst they stall the
-    // warp for that long; woven into the exponentials part of that time is hidden.
-    auto phase1 = [&](int t, bool drain, float *dq_dst) -> bool {
-      const int m0 = t_p1.mt * BM;
-      advance(t_p1);
+    int mt = mt_lo;   // query tile of the current tile
+
+    for (int t = 0; t < T_tiles; ++t) {
+      const int m0 = mt * BM;
+      if (++mt == mt_hi) mt = mt_lo;
       const bool q_ok = m0 + cg * 32 + lane < p.M;
       const float lse_lane = q_ok ? lse_next * kLog2e : INFINITY;
-      dlt_lane = q_ok ? dlt_next : 0.f;
+      const float dlt_lane = q_ok ? dlt_next : 0.f;
       if (t + 1 < T_tiles) fetch_stats();
+      // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
+      // masking at all; the others mask with one unsigned range check per element:
+      // column c is visible iff cmin <= c < cmin + cwidth.
       bool interior = (n0 + BN <= p.N) && (!p.causal || m0 + p_seq >= n0 + BN - 1);
       if (p.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
       if (p.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
@@ -340,116 +441,83 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       if (!key_ok) cmin = 32;
       const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
 
-      bool w_ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
-      if (w_ok && drain) w_ok = mbar_wait(bar(FB_DQ_FULL), (t - 1) & 1, actx, 915);
-      w_ok = __all_sync(0xffffffffu, w_ok);
-      if (!w_ok) return false;
+      // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
+      ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
-      uint32_t sr[32];
-      tmem_ld32(tlane + C::kColS + cg * 32, sr);
-      tmem_wait_ld();
-      uint32_t pk[16];
+      float pv[32];
+      {
+        uint32_t sr[32];
+        tmem_ld32(tlane + C::kColA + cg * 32, sr);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_S_LOADED));   // dP^T(t) may overwrite S^T(t)
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
-        uint32_t qr[QQ];
-        if (drain) {
-          if (QQ == 8) tmem_ld8(tlane + C::kColB + cg * QC + qd * QQ, qr);
-          else tmem_ld4(tlane + C::kColB + cg * QC + qd * QQ, qr);
-        }
-#pragma unroll
-        for (int c = 8 * qd; c < 8 * qd + 8; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const float lc = __shfl_sync(0xffffffffu, lse_lane, c);
           pv[c] = fmaf(__uint_as_float(sr[c]), qk_scale, -lc);
-          if (!interior) pv[c] = ((unsigned)(c - cmin) < cwidth) ? pv[c] : -INFINITY;  // exp2 -> 0
         }
+      }
+      if (!interior) {
 #pragma unroll
-        for (int c = 8 * qd; c < 8 * qd + 8; c += 2) {
+        for (int c = 0; c < 32; ++c)
+          pv[c] = ((unsigned)(c - cmin) < cwidth) ? pv[c] : -INFINITY;  // exp2(-inf) = 0
+      }
+      {
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
           pv[c] = ex2(pv[c]);
           pv[c + 1] = ex2(pv[c + 1]);
           pk[c >> 1] = TcElem<T>::pack(pv[c], pv[c + 1]);
         }
-        if (drain) {
-          tmem_wait_ld();
-          if (qd == 3) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(FB_DQ_FREE));   // dP^T of this tile may overwrite dQ
-          }
-          if (dq_dst) {
-#pragma unroll
-            for (int j = 0; j < QQ / 4; ++j)
-              red_add_v4(dq_dst + (int64_t)(qd * (QQ / 4) + j) * fp.Mpad * 4, qr[4 * j], qr[4 * j + 1],
-                         qr[4 * j + 2], qr[4 * j + 3]);
-          }
-        }
+        // PD still holds dS^T(t-1) until dQ(t-1) and dK(t-1) have read it
+        if (t > 0) ok = mbar_wait(bar(FB_DS_FREE), (t - 1) & 1, actx, 912);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        store_pd(pk);
       }
-      tmem_st16(tlane + C::kColS + cg * 32, pk);  // inside this thread's own columns
-      tmem_wait_st();
-      tc_fence_before();
+      fence_proxy_async_smem();   // the MMA reads PD through the async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_P1));
-      return true;
-    };
+      if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
 
-    if (T_tiles > 0) ok = phase1(0, false, nullptr);
-    for (int t = 0; t < T_tiles && ok; ++t) {
-      // ---- phase 2: dS^T = P^T * (dP^T - delta) into shared memory ----
+      // ---- phase 2: dS^T = P^T * (dP^T - delta) -> PD ----
       ok = mbar_wait(bar(FB_DP_FULL), t & 1, actx, 913);
-      if (ok && t > 0) ok = mbar_wait(bar(FB_DS_FREE), (t - 1) & 1, actx, 914);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       {
-        uint32_t sr[32];
-        tmem_ld32(tlane + C::kColB + cg * 32, sr);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float d0 = __shfl_sync(0xffffffffu, dlt_lane, c);
-          const float d1 = __shfl_sync(0xffffffffu, dlt_lane, c + 1);
-          pk[c >> 1] = TcElem<T>::pack(pv[c] * (__uint_as_float(sr[c]) - d0),
-                                       pv[c + 1] * (__uint_as_float(sr[c + 1]) - d1));
-        }
+        for (int hf = 0; hf < 2; ++hf) {   // two halves of 16 columns: fewer live registers
+          uint32_t sr[16];
+          tmem_ld16(tlane + C::kColA + cg * 32 + hf * 16, sr);
+          tmem_wait_ld();
+          if (hf == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // S^T(t+1) may overwrite dP^T(t)
+          }
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4 *>(ds_row + (((ds_chunk0 + j) ^ ds_xor) << 4)) =
-              make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-      }
-      fence_proxy_async_smem();   // the MMAs read dS^T through the async proxy
-      tc_fence_before();          // and dQ(t) overwrites the dP^T columns just read
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_P2));
-
-      // ---- phase 1 of the next tile, with the read-out of dQ(t) woven in ----
-      // dQ rows are queries: this thread owns row `row` of the tile and QC of its columns
-      const int m_t = t_cur.mt * BM + row;
-      float *dq_dst = nullptr;
-      if (m_t < p.M)
-        dq_dst = fp.dq_acc +
-                 (((int64_t)b * p.H + t_cur.h) * (D / 4) + cg * (QC / 4)) * (int64_t)fp.Mpad * 4 +
-                 (int64_t)m_t * 4;
-      advance(t_cur);
-      if (t + 1 < T_tiles) {
-        ok = phase1(t + 1, true, dq_dst);
-        if (!ok) break;
-      } else {
-        // last tile: plain read-out
-        ok = mbar_wait(bar(FB_DQ_FULL), t & 1, actx, 917);
+          for (int c = 0; c < 16; c += 2) {
+            const float d0 = __shfl_sync(0xffffffffu, dlt_lane, hf * 16 + c);
+            const float d1 = __shfl_sync(0xffffffffu, dlt_lane, hf * 16 + c + 1);
+            pk[hf * 8 + (c >> 1)] =
+                TcElem<T>::pack(pv[hf * 16 + c] * (__uint_as_float(sr[c]) - d0),
+                                pv[hf * 16 + c + 1] * (__uint_as_float(sr[c + 1]) - d1));
+          }
+        }
+        // PD still holds P^T(t) until dV(t) has read it
+        ok = mbar_wait(bar(FB_PT_FREE), t & 1, actx, 914);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        tc_fence_after();
-        uint32_t qr[QC];
-        if (QC == 32) tmem_ld32(tlane + C::kColB + cg * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
-        else tmem_ld16(tlane + C::kColB + cg * QC, qr);
-        tmem_wait_ld();
-        if (dq_dst) {
-#pragma unroll
-          for (int j = 0; j < QC / 4; ++j)
-            red_add_v4(dq_dst + (int64_t)j * fp.Mpad * 4, qr[4 * j], qr[4 * j + 1], qr[4 * j + 2],
-                       qr[4 * j + 3]);
-        }
+        store_pd(pk);
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FB_DS_FULL));
     }
 
     if (ok && T_tiles > 0) {
@@ -512,12 +580,14 @@ __global__ void __launch_bounds__(256)
   const int m = blockIdx.x * 32 + lane;
   const int h = blockIdx.y, b = blockIdx.z;
   if (m >= M) return;
-  const float *src = acc + ((int64_t)b * H + h) * (D / 4) * (int64_t)Mpad * 4 + (int64_t)m * 4;
+  // workspace layout (B, H, Mpad / 128, D / 4, 128, 4)
+  const float *src = acc + (((int64_t)b * H + h) * (Mpad / 128) + m / 128) * (int64_t)(128 * D) +
+                     (m % 128) * 4;
   T *orow = row_ptr_mut<T>(dq, sdq, b, h, m);
 #pragma unroll
   for (int g = w; g < D / 8; g += 8) {
-    const float4 lo = *reinterpret_cast<const float4 *>(src + (int64_t)(2 * g) * Mpad * 4);
-    const float4 hi = *reinterpret_cast<const float4 *>(src + (int64_t)(2 * g + 1) * Mpad * 4);
+    const float4 lo = *reinterpret_cast<const float4 *>(src + (2 * g) * 512);
+    const float4 hi = *reinterpret_cast<const float4 *>(src + (2 * g + 1) * 512);
     uint4 v;
     v.x = TcElem<T>::pack(lo.x * scale, lo.y * scale);
     v.y = TcElem<T>::pack(lo.z * scale, lo.w * scale);

@@ -421,6 +421,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     for (int t = 0; t < T_tiles; ++t) {
       const int m0 = mt * BM;
       if (++mt == mt_hi) mt = mt_lo;
+
+      // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
+      ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float pv[32];
+      uint32_t sr[32];
+      tmem_ld32(tlane + C::kColA + cg * 32, sr);
+      // while the load is in flight: this tile's statistics, the fetch of the next tile's, masks
       const bool q_ok = m0 + cg * 32 + lane < p.M;
       const float lse_lane = q_ok ? lse_next * kLog2e : INFINITY;
       const float dlt_lane = q_ok ? dlt_next : 0.f;
@@ -440,16 +450,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       }
       if (!key_ok) cmin = 32;
       const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
-
-      // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
-      ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      float pv[32];
       {
-        uint32_t sr[32];
-        tmem_ld32(tlane + C::kColA + cg * 32, sr);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();

@@ -33,7 +33,8 @@ template <typename T, int D>
 static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
                         const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                         const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
-                        const fa_tensor4 *dv, float *workspace, cudaStream_t stream) {
+                        const fa_tensor4 *dv, float *workspace, cudaStream_t stream, int mode = 0,
+                        int w = 0, int dv_accumulate = 0) {
   using C = FusedBwdCfg<D>;
   CUtensorMap mq, mdo, mk, mv;
   if (!make_map_bhld(&mq, q, s->dtype, s->B, s->H, s->M, D, C::BM) ||
@@ -50,6 +51,7 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
   p.B = s->B, p.H = s->H, p.Hk = s->Hk, p.M = s->M, p.N = s->N;
   p.causal = s->causal, p.sm_scale = s->sm_scale;
   p.status = device_status_word();
+  p.mode = mode, p.w = w, p.dv_accumulate = dv_accumulate;
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
   fp.dq_acc = workspace;
   fp.Mpad = (s->M + 127) / 128 * 128;
@@ -65,10 +67,53 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
   return FA_OK;
 }
 
+// piecewise_attention: the kernel runs once per branch (near pairs scored with q1.k1, far pairs
+// with q2.k2), each launch restricted to the tiles that hold a pair of its branch; dV is written
+// by the near launch and added to by the far one; the workspace serves both launches in turn.
+template <typename T, int D>
+static int launch_pw_fused(const fa_flash_shape *s, int w, const fa_tensor4 *q1, const fa_tensor4 *k1,
+                           const fa_tensor4 *q2, const fa_tensor4 *k2, const fa_tensor4 *v,
+                           const fa_tensor4 *d_o, const float *lse, const float *delta,
+                           const fa_tensor4 *dq1, const fa_tensor4 *dq2, const fa_tensor4 *dk1,
+                           const fa_tensor4 *dk2, const fa_tensor4 *dv, float *workspace,
+                           cudaStream_t stream) {
+  int st = launch_fused<T, D>(s, q1, k1, v, d_o, lse, delta, dq1, dk1, dv, workspace, stream, 1, w, 0);
+  if (st != FA_OK) return st;
+  return launch_fused<T, D>(s, q2, k2, v, d_o, lse, delta, dq2, dk2, dv, workspace, stream, 2, w, 1);
+}
+
 }  // namespace tc
 }  // namespace fa
 
 using namespace fa;
+
+extern "C" int fa_piecewise_bwd_fused(const fa_flash_shape *s, int32_t dist_threshold,
+                                      const fa_tensor4 *q1, const fa_tensor4 *k1,
+                                      const fa_tensor4 *q2, const fa_tensor4 *k2,
+                                      const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                                      const float *delta, const fa_tensor4 *dq1,
+                                      const fa_tensor4 *dq2, const fa_tensor4 *dk1,
+                                      const fa_tensor4 *dk2, const fa_tensor4 *dv, void *workspace,
+                                      int64_t workspace_bytes, void *stream) {
+  if (int st = validate_shape(s)) return st;
+  if (s->H != s->Hk) return FA_ERR_BAD_ARG;
+  if (int st = validate_tensors({q1, k1, q2, k2, v, d_o, dq1, dq2, dk1, dk2, dv})) return st;
+  if (!lse || !delta) return FA_ERR_BAD_ARG;
+  if (!tc::fused_covered(s) || dist_threshold > (1 << 29) || dist_threshold < -(1 << 29))
+    return FA_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < tc::fused_workspace_bytes(s) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return FA_ERR_WORKSPACE;
+  float *ws = static_cast<float *>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define FA_PWF_ARGS s, dist_threshold, q1, k1, q2, k2, v, d_o, lse, delta, dq1, dq2, dk1, dk2, dv, ws, st
+  if (s->dtype == FA_F16)
+    return s->D == 128 ? tc::launch_pw_fused<__half, 128>(FA_PWF_ARGS)
+                       : tc::launch_pw_fused<__half, 64>(FA_PWF_ARGS);
+  return s->D == 128 ? tc::launch_pw_fused<__nv_bfloat16, 128>(FA_PWF_ARGS)
+                     : tc::launch_pw_fused<__nv_bfloat16, 64>(FA_PWF_ARGS);
+#undef FA_PWF_ARGS
+}
 
 extern "C" int64_t fa_flash_bwd_fused_workspace_bytes(const fa_flash_shape *s) {
   if (!s || validate_shape(s) != FA_OK || !tc::fused_covered(s)) return 0;

@@ -4,6 +4,7 @@ Mirrors src/flag_attn/piecewise.py:25-191: score(m, n) = q2.k2 when the
 bottom-right-aligned distance (m + N - M) - n is at least `dist_threshold`,
 else q1.k1; returns the output only; gradients for the five tensors.
 """
+import ctypes
 import math
 
 import torch
@@ -66,6 +67,19 @@ class PiecewiseAttention(torch.autograd.Function):
             dk1 = torch.empty(k1.shape, dtype=k1.dtype, device=k1.device)
             dk2 = torch.empty(k2.shape, dtype=k2.dtype, device=k2.device)
             dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+            ws_bytes = lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+            if ws_bytes > 0:
+                # one pass per branch over the score tiles; dq1 / dq2 accumulate in an fp32 workspace
+                dq1 = torch.empty(q1.shape, dtype=q1.dtype, device=q1.device)
+                dq2 = torch.empty(q2.shape, dtype=q2.dtype, device=q2.device)
+                ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q1.device)
+                outs = [_C.tensor4(x) for x in (dq1, dq2, dk1, dk2, dv)]
+                st = lib.fa_piecewise_bwd_fused(_C.byref(shape), w, *[_C.byref(t) for t in ins],
+                                                _C.byref(tdo), _C.fptr(L), _C.fptr(delta),
+                                                *[_C.byref(t) for t in outs], _C.fptr(ws),
+                                                ctypes.c_int64(ws_bytes), stream)
+                _C.check(st, "fa_piecewise_bwd_fused")
+                return dq1, dk1, dq2, dk2, dv, None, None, None
             outs = [_C.tensor4(x) for x in (dk1, dk2, dv)]
             st = lib.fa_piecewise_bwd_dkdv(_C.byref(shape), w, *[_C.byref(t) for t in ins],
                                            _C.byref(tdo), _C.fptr(L), _C.fptr(delta),

@@ -173,6 +173,18 @@ int fa_piecewise_bwd_dq(const fa_flash_shape *s, int32_t dist_threshold, const f
                         const float *delta, const fa_tensor4 *dq1, const fa_tensor4 *dq2,
                         void *stream);
 
+/* All five gradients of piecewise_attention from one pass per branch over the score tiles: the
+ * counterpart of fa_flash_bwd_fused (same workspace size, from fa_flash_bwd_fused_workspace_bytes
+ * on the same shape; 0 = not covered, use fa_piecewise_bwd_dkdv + fa_piecewise_bwd_dq).
+ * Replaces the pair of launches at src/flag_attn/piecewise.py:114-164.  dq1, dq2 are
+ * reproducible to fp32 rounding only. */
+int fa_piecewise_bwd_fused(const fa_flash_shape *s, int32_t dist_threshold, const fa_tensor4 *q1,
+                           const fa_tensor4 *k1, const fa_tensor4 *q2, const fa_tensor4 *k2,
+                           const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                           const float *delta, const fa_tensor4 *dq1, const fa_tensor4 *dq2,
+                           const fa_tensor4 *dk1, const fa_tensor4 *dk2, const fa_tensor4 *dv,
+                           void *workspace, int64_t workspace_bytes, void *stream);
+
 /* ---------------------------------------------------------------------- */
 /* paged_attention (single-token decode over a block-table KV cache)       */
 /* ---------------------------------------------------------------------- */

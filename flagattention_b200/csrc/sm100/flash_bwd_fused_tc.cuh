@@ -455,10 +455,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(FB_S_LOADED));   // dP^T(t) may overwrite S^T(t)
+        // packed fp32 pairs: one FMA per two elements
+        const uint64_t scale2 = f2_pack(qk_scale, qk_scale);
+        const float nlse = -lse_lane;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float lc = __shfl_sync(0xffffffffu, lse_lane, c);
-          pv[c] = fmaf(__uint_as_float(sr[c]), qk_scale, -lc);
+        for (int c = 0; c < 32; c += 2) {
+          const float l0 = __shfl_sync(0xffffffffu, nlse, c);
+          const float l1 = __shfl_sync(0xffffffffu, nlse, c + 1);
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), scale2,
+                           f2_pack(l0, l1)),
+                    pv[c], pv[c + 1]);
         }
       }
       if (!interior) {
@@ -491,6 +497,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       tc_fence_after();
       {
         uint32_t pk[16];
+        const float ndlt = -dlt_lane;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {   // two halves of 16 columns: fewer live registers
           uint32_t sr[16];
@@ -503,11 +510,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           }
 #pragma unroll
           for (int c = 0; c < 16; c += 2) {
-            const float d0 = __shfl_sync(0xffffffffu, dlt_lane, hf * 16 + c);
-            const float d1 = __shfl_sync(0xffffffffu, dlt_lane, hf * 16 + c + 1);
-            pk[hf * 8 + (c >> 1)] =
-                TcElem<T>::pack(pv[hf * 16 + c] * (__uint_as_float(sr[c]) - d0),
-                                pv[hf * 16 + c + 1] * (__uint_as_float(sr[c + 1]) - d1));
+            const float d0 = __shfl_sync(0xffffffffu, ndlt, hf * 16 + c);
+            const float d1 = __shfl_sync(0xffffffffu, ndlt, hf * 16 + c + 1);
+            float e0, e1;   // P * (dP - delta), two elements per instruction
+            f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c], pv[hf * 16 + c + 1]),
+                             f2_add(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])),
+                                    f2_pack(d0, d1))),
+                      e0, e1);
+            pk[hf * 8 + (c >> 1)] = TcElem<T>::pack(e0, e1);
           }
         }
         // PD still holds P^T(t) until dV(t) has read it

@@ -263,13 +263,14 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
           if (c < lo || c >= hi) s[c] = -INFINITY;
       }
       // four independent chains instead of one 64-deep dependency chain
-      float mx4[4] = {s[0], s[1], s[2], s[3]};
+      // (three-input max: two new elements per instruction)
+      float mx4[4] = {fmaxf(s[0], s[1]), fmaxf(s[2], s[3]), fmaxf(s[4], s[5]), fmaxf(s[6], s[7])};
 #pragma unroll
-      for (int c = 4; c < BN; c += 4) {
-        mx4[0] = fmaxf(mx4[0], s[c]);
-        mx4[1] = fmaxf(mx4[1], s[c + 1]);
-        mx4[2] = fmaxf(mx4[2], s[c + 2]);
-        mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      for (int c = 8; c < BN; c += 8) {
+        mx4[0] = max3(mx4[0], s[c], s[c + 1]);
+        mx4[1] = max3(mx4[1], s[c + 2], s[c + 3]);
+        mx4[2] = max3(mx4[2], s[c + 4], s[c + 5]);
+        mx4[3] = max3(mx4[3], s[c + 6], s[c + 7]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx);
@@ -304,15 +305,22 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_ms = -m_eff * qk_scale;
       uint32_t pk[BN / 2];
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      // packed fp32 pairs: one FMA and one add per two elements
+      const uint64_t scale2 = f2_pack(qk_scale, qk_scale), shift2 = f2_pack(neg_ms, neg_ms);
+      uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < BN; c += 2) {
-        const float p0 = ex2(fmaf(s[c], qk_scale, neg_ms));
-        const float p1 = ex2(fmaf(s[c + 1], qk_scale, neg_ms));
-        rs4[(c >> 1) & 3] += p0 + p1;
+        float x0, x1;
+        f2_unpack(f2_fma(f2_pack(s[c], s[c + 1]), scale2, shift2), x0, x1);
+        const float p0 = ex2(x0), p1 = ex2(x1);
+        rs2[(c >> 1) & 3] = f2_add(rs2[(c >> 1) & 3], f2_pack(p0, p1));
         pk[c >> 1] = TcElem<T>::pack(p0, p1);
       }
-      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      {
+        float a0, a1;
+        f2_unpack(f2_add(f2_add(rs2[0], rs2[1]), f2_add(rs2[2], rs2[3])), a0, a1);
+        l += a0 + a1;
+      }
       tmem_st32(scol, reinterpret_cast<const uint32_t(&)[32]>(pk));
       tmem_wait_st();
       tc_fence_before();

@@ -343,6 +343,42 @@ def make_paged_inputs(device, seed):
     return q, kc, vc, lens, bt, blocks
 
 
+def run_decode(args, dist, rank, world, device):
+    """Single-query flash_attention over a long contiguous KV (the shape of the reference's
+    benchmark/flash_decoding_benchmark.py: B=2, H=2048/D, M=1, fp16, non-causal), device-resident."""
+    import flagattention_b200 as fa
+    B, D, N = 2, 128, 1 << 18
+    H = 2048 // D
+    gen = torch.Generator(device=device).manual_seed(10086 + 6 + rank)
+    q = torch.randn((B, H, 1, D), generator=gen, device=device).to(torch.float16)
+    k = torch.randn((B, H, N, D), generator=gen, device=device).to(torch.float16)
+    v = torch.randn((B, H, N, D), generator=gen, device=device).to(torch.float16)
+    for _ in range(max(3, args.warmup)):
+        fa.flash_attention(q, k, v)
+    steps = max(args.steps, 10)
+    barrier(dist)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fa.flash_attention(q, k, v)
+    t1.record()
+    torch.cuda.synchronize()
+    barrier(dist)
+    ms = max_over_ranks(dist, t0.elapsed_time(t1), device) / steps
+    algo_bytes = 2 * k.numel() * 2 + 2 * q.numel() * 2
+    gbs = world * algo_bytes / (ms * 1e-3) / 1e9
+    peaks = load_peaks()
+    return dict(metric="flash_attention single-query decode HBM GB/s", value=round(gbs, 1), unit="GB/s",
+                ms_per_step=round(ms, 4), algorithmic_bytes=algo_bytes,
+                config=dict(workload="flash_attention M=1 fp16 non-causal", B=B, H=H, N=N, D=D,
+                            l2="K and V (4.3 GB) are larger than L2"),
+                roofline=dict(bound="hbm", kernel="paged_decode_kernel+paged_reduce_kernel on K, V in place",
+                              achieved=round(gbs / world, 1), peak=peaks["hbm_gbs"], unit="GB/s",
+                              frac=round(gbs / world / peaks["hbm_gbs"], 4), peak_source=peaks["source"],
+                              traffic=None),
+                gpu_launches=2 * steps)
+
+
 def run_paged(args, dist, rank, world, device):
     import flagattention_b200 as fa
     c = PAGED_CFG
@@ -496,6 +532,7 @@ def main():
     fl = run_flash(args, dist, rank, world, device)
     paged = None if (args.skip_paged or args.only == "flash") else run_paged(args, dist, rank, world, device)
     pw = None if (args.skip_piecewise or args.only == "flash") else run_piecewise(args, dist, rank, world, device)
+    dec = None if (args.skip_paged or args.only == "flash") else run_decode(args, dist, rank, world, device)
     cpu = None
     if rank == 0 and not args.skip_cpu and world == 1:
         cpu, _ = cpu_flash_sample(2)
@@ -513,7 +550,7 @@ def main():
                        "l2": "inputs (4 x 128 MiB) are larger than the 126 MB L2"},
             "roofline": fl["roofline"], "cpu_baseline": cpu, "e2e": fl["e2e"],
             "gpu_launches": fl["launches"], "clocks": fl["clocks"], "paged": paged,
-            "piecewise": pw,
+            "piecewise": pw, "decode": dec,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

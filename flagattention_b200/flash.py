@@ -45,6 +45,89 @@ def _forward(q, k, v, causal, sm_scale, dropout_p=0.0, seed=0, offset=0):
     return o, L
 
 
+_identity_tables = {}
+
+
+def _identity_block_table(B, blocks_per_batch, id_stride, device):
+    """(block_tables, context_lens) with block_tables[b, c] = b * id_stride + c, cached: the block
+    table under which a (B, Hk, N, D) key tensor is, in place, a paged cache of 16-token blocks."""
+    key = (B, blocks_per_batch, id_stride, str(device))
+    tab = _identity_tables.get(key)
+    if tab is None:
+        if len(_identity_tables) >= 8:
+            _identity_tables.clear()
+        tab = (torch.arange(B, device=device, dtype=torch.int32)[:, None] * id_stride +
+               torch.arange(blocks_per_batch, device=device, dtype=torch.int32)[None, :]).contiguous()
+        lens = torch.full((B,), blocks_per_batch * 16, dtype=torch.int32, device=device)
+        tab = (tab, lens)
+        _identity_tables[key] = tab
+    return tab
+
+
+def _decode_covered(q, k, v):
+    """Single-query forward (M == 1) that the paged-decode kernels can run directly on k and v:
+    the keys of a batch element are then a block table of 16-token blocks in place."""
+    B, H, M, D = q.shape
+    N = k.shape[2]
+    if M != 1 or N % 16 != 0 or N == 0:
+        return False
+    if k.stride() != v.stride() or k.stride(3) != 1 or k.data_ptr() % 16 or v.data_ptr() % 16:
+        return False
+    sb, sh, sl, _ = k.stride()
+    if sl % 8 or sh % 8 or sb % (16 * sl) or (B * (sb // (16 * sl))) >= 2 ** 31:
+        return False
+    return True
+
+
+def _decode_forward(q, k, v, sm_scale):
+    """o for M == 1 through fa_paged_decode / fa_paged_reduce (an HBM-bound gather kernel that
+    streams K and V once), instead of the split-KV tile kernels."""
+    B, H, _, D = q.shape
+    Hk, N = k.shape[1], k.shape[2]
+    BS = 16
+    sb, sh, sl, _ = k.stride()
+    lib = _C.load()
+    num_sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+    # partitions of the key axis: enough (batch, kv head, partition) CTAs for about eight waves,
+    # each long enough (>= 256 keys) to amortise its pipeline fill
+    partition_size = 256
+    while partition_size < 8192 and B * Hk * (N // (2 * partition_size)) >= 8 * num_sms:
+        partition_size *= 2
+    if N <= partition_size:
+        partition_size = 0   # one pass, no reduction kernel
+    table, ctx_lens = _identity_block_table(B, N // BS, sb // (BS * sl), q.device)
+    q2 = q.reshape(B, H, D)
+    if q2.stride(-1) != 1 or q2.data_ptr() % 16 or q2.stride(0) % 8 or q2.stride(1) % 8:
+        q2 = q2.contiguous()
+    o = torch.empty((B, H, 1, D), dtype=q.dtype, device=q.device)
+    args = _C.PagedArgs()
+    args.dtype = _C.dtype_code(q.dtype)
+    args.num_seqs, args.num_q_heads, args.num_kv_heads = B, H, Hk
+    args.head_size, args.block_size = D, BS
+    args.max_context_len = N
+    args.block_table_is_i64 = 0
+    args.partition_size = partition_size
+    args.attn_scale = float(sm_scale)
+    args.query, args.q_stride_s, args.q_stride_h = q2.data_ptr(), q2.stride(0), q2.stride(1)
+    args.key_cache, args.value_cache = k.data_ptr(), v.data_ptr()
+    args.kv_stride_b, args.kv_stride_h, args.kv_stride_t = BS * sl, sh if Hk > 1 else 0, sl
+    args.context_lens = ctx_lens.data_ptr()
+    args.block_tables, args.bt_stride_s = table.data_ptr(), table.stride(0)
+    args.out, args.o_stride_s, args.o_stride_h = o.data_ptr(), H * D, D
+    stream = _C.stream_ptr(q.device)
+    if partition_size:
+        P = (N + partition_size - 1) // partition_size
+        part_out = torch.empty((B, H, P, D), dtype=torch.float32, device=q.device)
+        part_max = torch.empty((B, H, P), dtype=torch.float32, device=q.device)
+        part_sum = torch.empty_like(part_max)
+        args.part_out, args.part_max, args.part_sum = (part_out.data_ptr(), part_max.data_ptr(),
+                                                       part_sum.data_ptr())
+    _C.check(lib.fa_paged_decode(_C.byref(args), stream), "fa_paged_decode")
+    if partition_size:
+        _C.check(lib.fa_paged_reduce(_C.byref(args), stream), "fa_paged_reduce")
+    return o
+
+
 def _total_attention(q, k, L, causal, sm_scale):
     B, H, M, D = q.shape
     N, Hk = k.shape[2], k.shape[1]
@@ -129,6 +212,13 @@ class FlashAttention(torch.autograd.Function):
             sm_scale = 1. / math.sqrt(D)
 
         q, k, v = _C.kernel_ready(q), _C.kernel_ready(k), _C.kernel_ready(v)
+
+        has_extra_return = True in (return_log_normalizer, return_total_attention, return_seed_offset)
+        if (M == 1 and dropout_p == 0 and not has_extra_return and not any(ctx.needs_input_grad[:3])
+                and _decode_covered(q, k, v)):
+            # decode step without gradients: nothing but o is needed, K and V are streamed once
+            with torch.cuda.device(q.device):
+                return _decode_forward(q, k, v, sm_scale)
 
         with torch.cuda.device(q.device):
             # dropout: one Philox counter per element of the (B, H, M, N) attention matrix

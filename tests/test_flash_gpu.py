@@ -252,3 +252,44 @@ def test_device_status_word_is_clean():
     out = ctypes.c_int32(-1)
     assert _C.load().fa_device_status(ctypes.byref(out), 0) == 0
     assert out.value == 0
+
+
+@pytest.mark.parametrize("B,Hq,Hk,N,D", [(2, 16, 16, 4096, 128), (1, 8, 2, 1040, 64), (3, 4, 1, 16, 32),
+                                         (2, 32, 32, 65536, 64), (1, 4, 4, 8208, 16)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["BHTD", "BTHD"])
+def test_single_query_forward_streams_kv_in_place(B, Hq, Hk, N, D, dtype, layout):
+    """M == 1 without gradients or extra outputs runs on the paged-decode kernels, K and V read in
+    place through an identity block table (reference dispatch: src/flag_attn/flash.py:59-61 sends
+    these shapes to split-KV)."""
+    q, k, v, _ = make_qkv(B, Hq, Hk, 1, N, D, dtype, "cuda", 1.0, layout, seed=N + D)
+    from flagattention_b200 import flash as fl
+    assert fl._decode_covered(q, k, v)
+    o = fa.flash_attention(q, k, v, causal=True)
+    o_ref = oracle.flash_attention(q, k, v, True, upcast=True)
+    o_tor = oracle.flash_attention(q, k, v, True, upcast=False)
+    assert_within_2x(o, o_ref, o_tor, "o")
+    # the same call with an extra output takes the split-KV kernels: both paths agree
+    o2, lse, *_ = fa.flash_attention(q, k, v, causal=True, return_log_normalizer=True)
+    assert_within_2x(o2, o_ref, o_tor, "o (split-KV)")
+
+
+def test_single_query_forward_fallbacks():
+    """Ragged N, mismatched K/V strides or a gradient request keep the split-KV / tile kernels."""
+    from flagattention_b200 import flash as fl
+    q, k, v, _ = make_qkv(2, 4, 4, 1, 1000, 64, torch.float16, "cuda", seed=3)
+    assert not fl._decode_covered(q, k, v)          # 1000 % 16 != 0
+    o = fa.flash_attention(q, k, v)
+    assert_within_2x(o, oracle.flash_attention(q, k, v, False, upcast=True),
+                     oracle.flash_attention(q, k, v, False, upcast=False), "o")
+    q, k, v, do = make_qkv(2, 4, 4, 1, 1024, 64, torch.float16, "cuda", seed=4)
+    assert not fl._decode_covered(q, k, v.transpose(1, 2).contiguous().transpose(1, 2))
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = fa.flash_attention(q, k, v)
+    g = torch.autograd.grad(o, (q, k, v), do)
+    o_ref = oracle.flash_attention(q, k, v, False, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_tor = oracle.flash_attention(q, k, v, False, upcast=False)
+    g_tor = torch.autograd.grad(o_tor, (q, k, v), do)
+    for name, h, r, t in zip(("dq", "dk", "dv"), g, g_ref, g_tor):
+        assert_within_2x(h, r, t, name)

@@ -11,4 +11,5 @@ from .piecewise import attention as piecewise_attention  # noqa: F401
 from .flash import attention as flash_attention  # noqa: F401
 from .split_kv import attention as flash_attention_split_kv  # noqa: F401
 from .paged import attention as paged_attention  # noqa: F401
+from .paged import reshape_and_cache  # noqa: F401  (writer of the paged caches; no reference counterpart)
 from . import testing  # noqa: F401

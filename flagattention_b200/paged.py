@@ -8,7 +8,7 @@ import torch
 
 from . import _C
 
-__all__ = ["attention"]
+__all__ = ["attention", "reshape_and_cache"]
 
 
 def _next_power_of_2(n):
@@ -108,3 +108,34 @@ def attention(query, key_cache, value_cache, context_lens, block_tables, attn_sc
         if partition_size:
             _C.check(lib.fa_paged_reduce(_C.byref(args), stream), "fa_paged_reduce")
     return out
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
+    """Writes new tokens into the paged caches `attention` reads.
+
+    key, value: [num_tokens, kv_heads, head]; caches [num_blocks, kv_heads, block, head];
+    slot_mapping [num_tokens] integer: token i goes to block slot // block, position slot % block;
+    negative slots are skipped.  The reference has no writer (its tests fill the caches with random
+    numbers); a serving loop runs this step right before the decode kernel."""
+    import ctypes
+    num_tokens, num_kv_heads, head_size = key.shape
+    assert value.shape == key.shape and key_cache.shape == value_cache.shape
+    assert key_cache.shape[1] == num_kv_heads and key_cache.shape[3] == head_size
+    assert key.dtype == value.dtype == key_cache.dtype == value_cache.dtype
+    assert key_cache.stride() == value_cache.stride(), "key and value cache must share strides"
+    assert key_cache.stride(-1) == 1 and all(s % 8 == 0 for s in key_cache.stride()[:-1]), \
+        "caches need unit inner stride and 16-byte aligned rows"
+    assert slot_mapping.numel() == num_tokens
+    if key.stride() != value.stride() or key.stride(-1) != 1 or any(s % 8 for s in key.stride()[:-1]) \
+            or key.data_ptr() % 16 or value.data_ptr() % 16:
+        key, value = key.contiguous(), value.contiguous()
+    slots = slot_mapping.to(torch.int64).contiguous()
+    lib = _C.load()
+    with torch.cuda.device(key.device):
+        st = lib.fa_paged_cache_append(
+            _C.dtype_code(key.dtype), num_tokens, num_kv_heads, head_size, key_cache.shape[2],
+            _C.fptr(key), _C.fptr(value), ctypes.c_int64(key.stride(0)), ctypes.c_int64(key.stride(1)),
+            _C.fptr(key_cache), _C.fptr(value_cache), ctypes.c_int64(key_cache.stride(0)),
+            ctypes.c_int64(key_cache.stride(1)), ctypes.c_int64(key_cache.stride(2)),
+            _C.fptr(slots), _C.stream_ptr(key.device))
+    _C.check(st, "fa_paged_cache_append")

@@ -254,6 +254,22 @@ int64_t fa_paged_workspace_bytes(const fa_paged_args *a);
 #define FA_PAGED_NOALLOC_SCRATCH_BYTES 17039360 /* 32768 slots x (128 fp32 + 2 fp32) */
 int fa_paged_attention_noalloc(const fa_paged_args *a, void *stream);
 
+/* Writer of the caches fa_paged_decode reads: the key / value rows of `num_tokens` new tokens,
+ * (num_tokens, kv_heads, head) with element strides (src_stride_t, src_stride_h), go to
+ * cache[slot / block_size, :, slot % block_size, :] with slot = slot_mapping[token] (int64);
+ * tokens with a negative slot are skipped (padding).  Caches as in fa_paged_args, element
+ * strides (cache_stride_b, cache_stride_h, cache_stride_t); key and value (and the two caches)
+ * share strides; all strides multiples of 8, pointers 16-byte aligned, head a multiple of 8.
+ * The reference only reads such caches (layout: src/flag_attn/testing/paged.py:31-37; its tests
+ * and benchmark fill them with random numbers, tests/flag_attn/test_paged_attention.py:44-63);
+ * this is the caller-side step that produces them in a serving loop.  Bit-exact copy. */
+int fa_paged_cache_append(int32_t dtype, int32_t num_tokens, int32_t num_kv_heads,
+                          int32_t head_size, int32_t block_size, const void *key,
+                          const void *value, int64_t src_stride_t, int64_t src_stride_h,
+                          void *key_cache, void *value_cache, int64_t cache_stride_b,
+                          int64_t cache_stride_h, int64_t cache_stride_t,
+                          const int64_t *slot_mapping, void *stream);
+
 /* Test hook for "integer block-table indexing is bit-exact": writes, for
  * every (seq, logical block < ceil(context_len / block_size)), the physical
  * block id the decode kernel would gather from into visited[seq, block]

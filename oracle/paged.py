@@ -61,3 +61,15 @@ def paged_attention_gathered(query, key_cache, value_cache, block_tables, contex
         oi = torch.bmm(probs, values.float()).squeeze(1)
         out[i].copy_(oi.to(values.dtype))
     return out
+
+
+def cache_append(key, value, key_cache, value_cache, slot_mapping):
+    """Token-by-token restatement of the paged-cache writer (the layout paged_attention reads:
+    src/flag_attn/testing/paged.py:31-37).  The reference has no writer, so this has no fixture of
+    its own; the round trip append -> paged_attention is held to the pinned read-side oracle."""
+    block = key_cache.shape[2]
+    for i, slot in enumerate(slot_mapping.tolist()):
+        if slot < 0:
+            continue
+        key_cache[slot // block, :, slot % block, :] = key[i]
+        value_cache[slot // block, :, slot % block, :] = value[i]

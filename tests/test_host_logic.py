@@ -119,3 +119,20 @@ def test_public_api_surface():
     sig = inspect.signature(fa.paged_attention)
     assert list(sig.parameters) == ["query", "key_cache", "value_cache", "context_lens",
                                     "block_tables", "attn_scale", "max_context_len", "num_splits"]
+
+
+def test_single_query_dispatch_rule():
+    """Which (q, k, v) the single-query forward may hand to the paged-decode kernels in place."""
+    import torch
+    from flagattention_b200 import flash as fl
+    q = torch.zeros(2, 8, 1, 64, dtype=torch.float16)
+    k = torch.zeros(2, 2, 1024, 64, dtype=torch.float16)
+    v = torch.zeros(2, 2, 1024, 64, dtype=torch.float16)
+    assert fl._decode_covered(q, k, v)
+    assert not fl._decode_covered(torch.zeros(2, 8, 2, 64, dtype=torch.float16), k, v)      # M != 1
+    assert not fl._decode_covered(q, k[:, :, :1000], v[:, :, :1000])                        # N % 16 != 0
+    kt = torch.zeros(2, 1024, 2, 64, dtype=torch.float16).transpose(1, 2)                   # BTHD view
+    assert fl._decode_covered(q, kt, kt.clone(memory_format=torch.preserve_format))
+    assert not fl._decode_covered(q, kt, v)                                                 # strides differ
+    tab, lens = fl._identity_block_table(2, 4, 16, "cpu")
+    assert tab.tolist() == [[0, 1, 2, 3], [16, 17, 18, 19]] and lens.tolist() == [64, 64]

@@ -90,4 +90,5 @@ def test_append_then_decode_round_trip(dtype):
             v_s = vals[s][:cur[s]].float().repeat_interleave(Hq // Hk, dim=1)
             p = torch.softmax(torch.einsum("hd,thd->ht", q[s].float(), k_s) * D ** -0.5, dim=-1)
             o_s = torch.einsum("ht,thd->hd", p, v_s)
-            torch.testing.assert_close(out[s].float(), o_s, atol=1e-2, rtol=1e-2)
+            tol = 1e-2 if dtype == torch.float16 else 4e-2   # one 16-bit rounding step of the output
+            torch.testing.assert_close(out[s].float(), o_s, atol=tol, rtol=tol)

@@ -220,6 +220,10 @@ __global__ void __launch_bounds__(BM / 16 * 32) dense_fwd_kernel(const FwdParams
     __syncthreads();
   }
   cp_async_wait<0>();
+  // The epilogue stages O in the Q tile.  With no key tile to visit the loop above never ran its
+  // barrier, and another thread's asynchronous copy of Q could still land in this warp's rows
+  // after the staged O: wait for everybody's copies first.
+  if (num_tiles == 0) __syncthreads();
 
   // ---- epilogue ------------------------------------------------------------
   float inv[2], lse[2];

@@ -13,6 +13,7 @@
 //   warp 1       MMA issuer (one thread); every MMA is 128 x 128 x 16 (128 x 64 x 16 at D = 64)
 //   warps 2..17  element-wise stage, one thread per (accumulator row, 32 columns)
 //   warps 18..21 dQ reduction: TMEM -> shared-memory staging -> cp.reduce.async.bulk
+//   warp 22      stages lse / delta of every tile in shared memory
 //
 // TMEM (512 columns):  S^T, then dP^T | dQ | dK | dV.
 //   The two score products of a tile share one 128-column region: dP^T is issued as soon as the
@@ -48,7 +49,8 @@ struct FusedBwdCfg {
   static constexpr int kStage = kPD + kPdBytes;
   static constexpr int kBars = kStage + 2 * kQuarter;
   static constexpr int kMisc = kBars + 24 * 8;
-  static constexpr int kTotal = kMisc + 16 + 1024;
+  static constexpr int kStats = kMisc + 16;            // -lse*log2e [128] | -delta [128] of a tile
+  static constexpr int kTotal = kStats + 2 * 128 * 4 + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColA = 0, kColQ = 128, kColDK = 256, kColDV = 256 + D;
   static_assert(kTotal <= 232448, "shared memory budget");
@@ -57,7 +59,7 @@ struct FusedBwdCfg {
 enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB_DO_FREE = 7,
                 FB_S_FULL = 9, FB_S_LOADED = 10, FB_DP_FULL = 11, FB_DP_LOADED = 12,
                 FB_PT_FULL = 13, FB_PT_FREE = 14, FB_DS_FULL = 15, FB_DS_FREE = 16,
-                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19 };
+                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19, FB_LSE_FULL = 20, FB_DLT_FULL = 21 };
 
 struct FusedBwdParams {
   BwdTcParams base;
@@ -101,8 +103,8 @@ __device__ __forceinline__ bool red_warps_all(bool ok) {
 }
 
 // warps: 0 TMA producer, 1 MMA issuer, 2..17 element-wise, 18..21 dQ reduction (one per TMEM
-// lane slice)
-constexpr int kFusedThreads = kBwdThreads + 4 * 32;   // 704
+// lane slice), 22 statistics
+constexpr int kFusedThreads = kBwdThreads + 5 * 32;   // 736
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kFusedThreads, 1)
@@ -164,6 +166,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     mbar_init(bar(FB_DQ_FULL), 1);
     mbar_init(bar(FB_DQ_FREE), 4);
     mbar_init(bar(FB_DONE), 1);
+    mbar_init(bar(FB_LSE_FULL), 1);
+    mbar_init(bar(FB_DLT_FULL), 1);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -324,6 +328,41 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         mbar_wait(bar(FB_DONE), 0, actx, 819);
       }
     }
+  } else if (warp == 2 + kEwWarps + 4) {
+    // ------------------------------ statistics warp ----------------------------
+    // -lse * log2(e) and -delta of the 128 queries of every tile go through shared memory, where
+    // the element-wise threads read them as broadcast vectors (every thread needs the values of
+    // all its 32 query columns; fetching them lane by lane and shuffling costs 64 shuffles per
+    // thread and tile in a load/store queue that is already the busiest unit).  Queries past M
+    // get lse = +inf, which makes their P exactly zero.  One buffer each: lse(t) may be written
+    // once phase 1 of tile t - 1 is over, delta(t) once phase 2 of tile t - 1 is.
+    float4 *lse_s = reinterpret_cast<float4 *>(smem_gen + C::kStats);
+    float4 *dlt_s = lse_s + 32;
+    int h = hk * G, mt = mt_lo;
+    bool ok = true;
+    for (int t = 0; t < T_tiles; ++t) {
+      const int m = mt * BM + lane * 4;
+      const int64_t li = ((int64_t)b * p.H + h) * p.M + m;
+      if (++mt == mt_hi) mt = mt_lo, ++h;
+      float l[4], d[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        l[j] = m + j < p.M ? -p.lse[li + j] * kLog2e : -INFINITY;
+        d[j] = m + j < p.M ? -p.delta[li + j] : 0.f;
+      }
+      if (t > 0) ok = mbar_wait(bar(FB_PT_FULL), (t - 1) & 1, actx, 951);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      lse_s[lane] = make_float4(l[0], l[1], l[2], l[3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FB_LSE_FULL));
+      if (t > 0) ok = mbar_wait(bar(FB_DS_FULL), (t - 1) & 1, actx, 952);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      dlt_s[lane] = make_float4(d[0], d[1], d[2], d[3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FB_DLT_FULL));
+    }
   } else if (warp >= 2 + kEwWarps) {
     // ------------------------------ dQ reduction warps --------------------------
     // dQ(t) = dS K is a complete 128 x D product per tile.  These four warps (one per TMEM lane
@@ -401,21 +440,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     };
     bool ok = true;
 
-    // Lane c holds lse / delta of query column c of this thread's 32 columns (the loops below
-    // broadcast them with shuffles); queries past M get lse = +inf, which makes their P exactly
-    // zero.  The values of a tile are fetched one tile ahead, so their latency is off the
-    // critical path.
-    float lse_next = INFINITY, dlt_next = 0.f;
-    int h_f = hk * G, mt_f = mt_lo;   // tile whose statistics are fetched next
-    auto fetch_stats = [&]() {
-      const int qm_lane = mt_f * BM + cg * 32 + lane;
-      const int64_t li = ((int64_t)b * p.H + h_f) * p.M + min(qm_lane, p.M - 1);
-      // volatile: the loads must be issued here, a tile ahead of their use
-      asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(lse_next) : "l"(p.lse + li));
-      asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(dlt_next) : "l"(p.delta + li));
-      if (++mt_f == mt_hi) mt_f = mt_lo, ++h_f;
-    };
-    if (T_tiles > 0) fetch_stats();
+    // -lse * log2(e) / -delta of this thread's 32 query columns, as staged by the statistics warp
+    const float4 *lse_s = reinterpret_cast<const float4 *>(smem_gen + C::kStats) + cg * 8;
+    const float4 *dlt_s = lse_s + 32;
     int mt = mt_lo;   // query tile of the current tile
 
     for (int t = 0; t < T_tiles; ++t) {
@@ -423,18 +450,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       if (++mt == mt_hi) mt = mt_lo;
 
       // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
-      ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
+      ok = mbar_wait(bar(FB_LSE_FULL), t & 1, actx, 910);
+      if (ok) ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       float pv[32];
       uint32_t sr[32];
       tmem_ld32(tlane + C::kColA + cg * 32, sr);
-      // while the load is in flight: this tile's statistics, the fetch of the next tile's, masks
-      const bool q_ok = m0 + cg * 32 + lane < p.M;
-      const float lse_lane = q_ok ? lse_next * kLog2e : INFINITY;
-      const float dlt_lane = q_ok ? dlt_next : 0.f;
-      if (t + 1 < T_tiles) fetch_stats();
+      // while the load is in flight: the masks
       // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
       // masking at all; the others mask with one unsigned range check per element:
       // column c is visible iff cmin <= c < cmin + cwidth.
@@ -457,14 +481,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         if (lane == 0) mbar_arrive(bar(FB_S_LOADED));   // dP^T(t) may overwrite S^T(t)
         // packed fp32 pairs: one FMA per two elements
         const uint64_t scale2 = f2_pack(qk_scale, qk_scale);
-        const float nlse = -lse_lane;
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float l0 = __shfl_sync(0xffffffffu, nlse, c);
-          const float l1 = __shfl_sync(0xffffffffu, nlse, c + 1);
-          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), scale2,
-                           f2_pack(l0, l1)),
-                    pv[c], pv[c + 1]);
+        for (int i = 0; i < 8; ++i) {
+          const float4 l4 = lse_s[i];
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[4 * i]), __uint_as_float(sr[4 * i + 1])), scale2,
+                           f2_pack(l4.x, l4.y)),
+                    pv[4 * i], pv[4 * i + 1]);
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[4 * i + 2]), __uint_as_float(sr[4 * i + 3])),
+                           scale2, f2_pack(l4.z, l4.w)),
+                    pv[4 * i + 2], pv[4 * i + 3]);
         }
       }
       if (!interior) {
@@ -491,13 +516,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
 
       // ---- phase 2: dS^T = P^T * (dP^T - delta) -> PD ----
-      ok = mbar_wait(bar(FB_DP_FULL), t & 1, actx, 913);
+      ok = mbar_wait(bar(FB_DLT_FULL), t & 1, actx, 909);
+      if (ok) ok = mbar_wait(bar(FB_DP_FULL), t & 1, actx, 913);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       {
         uint32_t pk[16];
-        const float ndlt = -dlt_lane;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {   // two halves of 16 columns: fewer live registers
           uint32_t sr[16];
@@ -509,15 +534,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // S^T(t+1) may overwrite dP^T(t)
           }
 #pragma unroll
-          for (int c = 0; c < 16; c += 2) {
-            const float d0 = __shfl_sync(0xffffffffu, ndlt, hf * 16 + c);
-            const float d1 = __shfl_sync(0xffffffffu, ndlt, hf * 16 + c + 1);
-            float e0, e1;   // P * (dP - delta), two elements per instruction
+          for (int i = 0; i < 4; ++i) {   // P * (dP - delta), two elements per instruction
+            const float4 d4 = dlt_s[hf * 4 + i];
+            const int c = 4 * i;
+            float e0, e1, e2, e3;
             f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c], pv[hf * 16 + c + 1]),
                              f2_add(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])),
-                                    f2_pack(d0, d1))),
+                                    f2_pack(d4.x, d4.y))),
                       e0, e1);
-            pk[hf * 8 + (c >> 1)] = TcElem<T>::pack(e0, e1);
+            f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c + 2], pv[hf * 16 + c + 3]),
+                             f2_add(f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])),
+                                    f2_pack(d4.z, d4.w))),
+                      e2, e3);
+            pk[hf * 8 + 2 * i] = TcElem<T>::pack(e0, e1);
+            pk[hf * 8 + 2 * i + 1] = TcElem<T>::pack(e2, e3);
           }
         }
         // PD still holds P^T(t) until dV(t) has read it

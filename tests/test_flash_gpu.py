@@ -293,3 +293,20 @@ def test_single_query_forward_fallbacks():
     g_tor = torch.autograd.grad(o_tor, (q, k, v), do)
     for name, h, r, t in zip(("dq", "dk", "dv"), g, g_ref, g_tor):
         assert_within_2x(h, r, t, name)
+
+
+@pytest.mark.parametrize("generic", ["1", "0"])
+def test_rows_without_visible_keys_are_exact_zeros_every_time(generic, monkeypatch):
+    """M > N causal: CTAs whose rows see no key run no main-loop iteration.  Their output rows must
+    be exact zeros (lse = -inf) on every run, whatever the freed memory they reuse holds (the
+    shape-generic forward once let a late asynchronous copy of Q land in its staged output)."""
+    monkeypatch.setenv("FLAGATTN_B200_GENERIC", generic)
+    B, Hq, Hk, M, N, D = 2, 4, 2, 10006, 10, 128
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, torch.bfloat16, "cuda", 1.0, "BHTD", seed=M + D)
+    for rep in range(12):
+        junk = torch.full((48 << 20,), float("nan") if rep % 2 else 3.0, device="cuda", dtype=torch.bfloat16)
+        del junk
+        o, L, *_ = fa.flash_attention(q, k, v, True, return_log_normalizer=True)
+        assert torch.count_nonzero(o[:, :, :M - N]).item() == 0
+        assert torch.isinf(L[:, :, :M - N]).all() and (L[:, :, :M - N] < 0).all()
+        assert torch.isfinite(o).all() and torch.isfinite(L[:, :, M - N:]).all()

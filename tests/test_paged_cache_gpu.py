@@ -83,7 +83,9 @@ def test_append_then_decode_round_trip(dtype):
         ctx = torch.tensor(cur, dtype=torch.int32, device="cuda")
         out = fa.paged_attention(q, kc, vc, ctx, bt, D ** -0.5, max(cur))
         ref = oracle.paged_attention(q, kc, vc, bt, ctx, D ** -0.5)
-        torch.testing.assert_close(out, ref, atol=2e-3, rtol=1e-5)
+        # the reference's bar for fp16 (tests/flag_attn/test_paged_attention.py there); one bf16
+        # rounding step of an O(1) output is 2^-8
+        torch.testing.assert_close(out, ref, atol=2e-3 if dtype == torch.float16 else 8e-3, rtol=1e-5)
         # and against the tokens themselves, never having gone through a cache
         for s in range(seqs):
             k_s = keys[s][:cur[s]].float().repeat_interleave(Hq // Hk, dim=1)   # (ctx, Hq, D)

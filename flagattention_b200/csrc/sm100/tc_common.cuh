@@ -74,7 +74,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ---------------------------------------------------------------------------
-// TMA: 4-D tiled load global -> shared, completion on an mbarrier (no multicast)
+// TMA: 4-D tiled load global -> shared of this CTA only, completion on an mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap *map,
                                             uint32_t bar, int c0, int c1, int c2, int c3) {

@@ -241,28 +241,45 @@ def run_flash(args, dist, rank, world, device):
     e2e_steps = max(2, min(args.steps, 5))
     outs_host = [torch.empty((B, H, L, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
 
-    # The step is pipelined over (batch element, group of 8 heads) chunks on three streams, so that
-    # the host-to-device copy of one chunk overlaps the kernels of another and the device-to-host
-    # copy of a third: both PCIe directions stay busy and the fill / drain of the pipeline is one
-    # chunk (1/16 of the step), not one batch element.
-    streams = [torch.cuda.Stream(device=device) for _ in range(3)]
+    # The step is a three-stage pipeline over (batch element, group of 8 heads) chunks: one stream
+    # copies chunk i+1 in while a second runs the kernels of chunk i and a third copies the
+    # results of chunk i-1 out, so both PCIe directions and the SMs stay busy; the fill and drain
+    # of the pipeline are one chunk (1/16 of the step) each.
+    s_in, s_cmp, s_out = (torch.cuda.Stream(device=device) for _ in range(3))
     HG = 8 if H % 8 == 0 else H
     chunks = [(bi, h0) for bi in range(B) for h0 in range(0, H, HG)]
+    NS = 4   # input slots on the device
+    slots = [[torch.empty((1, HG, L, D), dtype=torch.bfloat16, device=device) for _ in range(4)]
+             for _ in range(NS)]
 
     def e2e_step():
         cur = torch.cuda.current_stream(device)
-        for st in streams:
+        for st in (s_in, s_cmp, s_out):
             st.wait_stream(cur)
+        slot_free = [None] * NS
         for ci, (bi, h0) in enumerate(chunks):
-            st = streams[ci % len(streams)]
-            with torch.cuda.stream(st):
-                qd, kd, vd, dod = (t[bi:bi + 1, h0:h0 + HG].to(device, non_blocking=True) for t in host)
-                qd.requires_grad_(), kd.requires_grad_(), vd.requires_grad_()
+            bufs = slots[ci % NS]
+            with torch.cuda.stream(s_in):
+                if slot_free[ci % NS] is not None:
+                    s_in.wait_event(slot_free[ci % NS])
+                for dst, src in zip(bufs, host):
+                    dst.copy_(src[bi:bi + 1, h0:h0 + HG], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in)
+                qd, kd, vd = (t.detach().requires_grad_() for t in bufs[:3])
                 o = fa.flash_attention(qd, kd, vd, causal=True)
-                grads = torch.autograd.grad(o, (qd, kd, vd), dod)
+                grads = torch.autograd.grad(o, (qd, kd, vd), bufs[3])
+                ev_cmp = torch.cuda.Event()
+                ev_cmp.record(s_cmp)
+                slot_free[ci % NS] = ev_cmp
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp)
                 for dst, src in zip(outs_host, (o.detach(), *grads)):
+                    src.record_stream(s_out)
                     dst[bi:bi + 1, h0:h0 + HG].copy_(src, non_blocking=True)
-        for st in streams:
+        for st in (s_in, s_cmp, s_out):
             cur.wait_stream(st)
 
     e2e_step()

@@ -218,8 +218,9 @@ def run_flash(args, dist, rank, world, device):
     per_kernel = {n: t / args.steps for n, t in per_kernel.items()}
 
     # executed GEMMs per kernel (each 2*B*H*M*N*D*0.5 FLOP with the causal half): fwd 2; the
-    # one-pass backward ("dkdvdq": zero-fill of the fp32 dq workspace, the kernel, the dq
-    # conversion) 5; where the backward runs as two kernels, dkdv 4 and dq 3
+    # one-pass backward kernel ("dkdvdq"; the zero-fill of its fp32 dq workspace and the dq
+    # conversion are timed apart as "dq_zero" and "dq_convert") 5; where the backward runs as two
+    # kernels, dkdv 4 and dq 3
     gemm = 2.0 * B * H * L * L * D * 0.5
     algo = dict(fwd=2 * gemm, dkdv=4 * gemm, dq=3 * gemm, dkdvdq=5 * gemm)
     algo = {n: f for n, f in algo.items() if n in per_kernel}
@@ -229,7 +230,11 @@ def run_flash(args, dist, rank, world, device):
     roofline = dict(bound="tensor", kernel=dominant, achieved=round(achieved, 2),
                     peak=peaks["tflops_sustained"], unit="TFLOP/s",
                     frac=round(achieved / peaks["tflops_sustained"], 4),
-                    peak_source=peaks["source"] + " (sustained cuBLAS bf16)", traffic=None,
+                    peak_source=peaks["source"] + " (sustained cuBLAS bf16)",
+                    # DRAM bytes of one launch of that kernel, from the ncu captures summarised under
+                    # profiles/ (not measured by this run)
+                    traffic={"dkdvdq": 1.304e9, "dkdv": 0.782e9, "dq": 0.662e9, "fwd": 0.522e9}.get(dominant),
+                    traffic_unit="bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, ncu)",
                     kernel_ms={n: round(t, 4) for n, t in per_kernel.items()},
                     kernel_tflops={n: round(algo[n] / (per_kernel[n] * 1e-3) / 1e12, 2) for n in algo})
 

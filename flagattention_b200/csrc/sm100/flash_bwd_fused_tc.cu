@@ -34,7 +34,7 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
                         const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                         const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
                         const fa_tensor4 *dv, float *workspace, cudaStream_t stream, int mode = 0,
-                        int w = 0, int dv_accumulate = 0) {
+                        int w = 0, int dv_accumulate = 0, int stages = 7) {
   using C = FusedBwdCfg<D>;
   CUtensorMap mq, mdo, mk, mv;
   if (!make_map_bhld(&mq, q, s->dtype, s->B, s->H, s->M, D, C::BM) ||
@@ -55,15 +55,21 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
   fp.dq_acc = workspace;
   fp.Mpad = (s->M + 127) / 128 * 128;
-  if (cudaMemsetAsync(workspace, 0, (size_t)fused_workspace_bytes(s), stream) != cudaSuccess)
+  // stages: 1 = zero-fill of the workspace, 2 = the kernel, 4 = scale + convert the workspace to dq
+  if ((stages & 1) &&
+      cudaMemsetAsync(workspace, 0, (size_t)fused_workspace_bytes(s), stream) != cudaSuccess)
     return FA_ERR_LAUNCH;
-  dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
-  kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, fp);
-  FA_CHECK_LAUNCH();
-  dim3 cgrid((s->M + 31) / 32, s->H, s->B);
-  dq_convert_kernel<T, D><<<cgrid, 256, 0, stream>>>(workspace, dq->ptr, strides_of(dq), s->H,
-                                                     s->M, fp.Mpad, s->sm_scale);
-  FA_CHECK_LAUNCH();
+  if (stages & 2) {
+    dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
+    kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, fp);
+    FA_CHECK_LAUNCH();
+  }
+  if (stages & 4) {
+    dim3 cgrid((s->M + 31) / 32, s->H, s->B);
+    dq_convert_kernel<T, D><<<cgrid, 256, 0, stream>>>(workspace, dq->ptr, strides_of(dq), s->H,
+                                                       s->M, fp.Mpad, s->sm_scale);
+    FA_CHECK_LAUNCH();
+  }
   return FA_OK;
 }
 
@@ -120,11 +126,29 @@ extern "C" int64_t fa_flash_bwd_fused_workspace_bytes(const fa_flash_shape *s) {
   return tc::fused_workspace_bytes(s);
 }
 
+extern "C" int fa_flash_bwd_fused_stages(const fa_flash_shape *s, const fa_tensor4 *q,
+                                         const fa_tensor4 *k, const fa_tensor4 *v,
+                                         const fa_tensor4 *d_o, const float *lse, const float *delta,
+                                         const fa_tensor4 *dq, const fa_tensor4 *dk,
+                                         const fa_tensor4 *dv, void *workspace,
+                                         int64_t workspace_bytes, int32_t stages, void *stream);
+
 extern "C" int fa_flash_bwd_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
                                   const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                                   const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
                                   const fa_tensor4 *dv, void *workspace, int64_t workspace_bytes,
                                   void *stream) {
+  return fa_flash_bwd_fused_stages(s, q, k, v, d_o, lse, delta, dq, dk, dv, workspace,
+                                   workspace_bytes, 7, stream);
+}
+
+extern "C" int fa_flash_bwd_fused_stages(const fa_flash_shape *s, const fa_tensor4 *q,
+                                         const fa_tensor4 *k, const fa_tensor4 *v,
+                                         const fa_tensor4 *d_o, const float *lse, const float *delta,
+                                         const fa_tensor4 *dq, const fa_tensor4 *dk,
+                                         const fa_tensor4 *dv, void *workspace,
+                                         int64_t workspace_bytes, int32_t stages, void *stream) {
+  if (stages < 1 || stages > 7) return FA_ERR_BAD_ARG;
   if (int st = validate_shape(s)) return st;
   if (int st = validate_tensors({q, k, v, d_o, dq, dk, dv})) return st;
   if (!lse || !delta) return FA_ERR_BAD_ARG;
@@ -134,7 +158,7 @@ extern "C" int fa_flash_bwd_fused(const fa_flash_shape *s, const fa_tensor4 *q, 
     return FA_ERR_WORKSPACE;
   float *ws = static_cast<float *>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define FA_FUSED_ARGS s, q, k, v, d_o, lse, delta, dq, dk, dv, ws, st
+#define FA_FUSED_ARGS s, q, k, v, d_o, lse, delta, dq, dk, dv, ws, st, 0, 0, 0, stages
   if (s->dtype == FA_F16)
     return s->D == 128 ? tc::launch_fused<__half, 128>(FA_FUSED_ARGS)
                        : tc::launch_fused<__half, 64>(FA_FUSED_ARGS);

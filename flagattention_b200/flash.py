@@ -169,13 +169,16 @@ def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None, dropout_p=0.0, see
         if ws_bytes > 0:
             # one pass over the score tiles; dq is accumulated in an fp32 workspace
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-            st = lib.fa_flash_bwd_fused(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
-                                        _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdq),
-                                        _C.byref(tdk), _C.byref(tdv), _C.fptr(ws),
-                                        ctypes.c_int64(ws_bytes), stream)
-            _C.check(st, "fa_flash_bwd_fused")
+            args = (_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv), _C.byref(tdo),
+                    _C.fptr(L), _C.fptr(delta), _C.byref(tdq), _C.byref(tdk), _C.byref(tdv),
+                    _C.fptr(ws), ctypes.c_int64(ws_bytes))
             if mark:
-                mark("dkdvdq")
+                # the three parts of the call one by one, so that each can be timed
+                for stage, name in ((1, "dq_zero"), (2, "dkdvdq"), (4, "dq_convert")):
+                    _C.check(lib.fa_flash_bwd_fused_stages(*args, stage, stream), "fa_flash_bwd_fused_stages")
+                    mark(name)
+            else:
+                _C.check(lib.fa_flash_bwd_fused(*args, stream), "fa_flash_bwd_fused")
             return dq, dk, dv
         st = lib.fa_flash_bwd_dkdv(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
                                    _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdk),

@@ -173,6 +173,15 @@ int fa_piecewise_bwd_dq(const fa_flash_shape *s, int32_t dist_threshold, const f
                         const float *delta, const fa_tensor4 *dq1, const fa_tensor4 *dq2,
                         void *stream);
 
+/* The same call in parts, for callers that time or interleave them: `stages` is a bit mask of
+ * 1 = zero-fill of the workspace, 2 = the kernel, 4 = scale and convert the workspace into dq;
+ * they must run in that order on one stream.  fa_flash_bwd_fused(...) = stages 7. */
+int fa_flash_bwd_fused_stages(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                              const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
+                              const float *delta, const fa_tensor4 *dq, const fa_tensor4 *dk,
+                              const fa_tensor4 *dv, void *workspace, int64_t workspace_bytes,
+                              int32_t stages, void *stream);
+
 /* All five gradients of piecewise_attention from one pass per branch over the score tiles: the
  * counterpart of fa_flash_bwd_fused (same workspace size, from fa_flash_bwd_fused_workspace_bytes
  * on the same shape; 0 = not covered, use fa_piecewise_bwd_dkdv + fa_piecewise_bwd_dq).

@@ -511,30 +511,25 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         if (!ok) break;
         store_pd(pk);
       }
-      fence_proxy_async_smem();   // the MMA reads PD through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
-
       // ---- phase 2: dS^T = P^T * (dP^T - delta) -> PD ----
+      // Its operands are there by now (dP^T(t) was issued as soon as S^T(t) had been read), so the
+      // first TMEM load goes out before the proxy fence of phase 1 and hides behind it.
       ok = mbar_wait(bar(FB_DLT_FULL), t & 1, actx, 909);
       if (ok) ok = mbar_wait(bar(FB_DP_FULL), t & 1, actx, 913);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      uint32_t sr0[16];
+      tmem_ld16(tlane + C::kColA + cg * 32, sr0);
+      fence_proxy_async_smem();   // the MMA reads PD through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
       {
         uint32_t pk[16];
+        // P * (dP - delta) of 16 columns, two elements per instruction
+        auto half_ds = [&](int hf, const uint32_t (&sr)[16]) {
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {   // two halves of 16 columns: fewer live registers
-          uint32_t sr[16];
-          tmem_ld16(tlane + C::kColA + cg * 32 + hf * 16, sr);
-          tmem_wait_ld();
-          if (hf == 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // S^T(t+1) may overwrite dP^T(t)
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {   // P * (dP - delta), two elements per instruction
+          for (int i = 0; i < 4; ++i) {
             const float4 d4 = dlt_s[hf * 4 + i];
             const int c = 4 * i;
             float e0, e1, e2, e3;
@@ -549,6 +544,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             pk[hf * 8 + 2 * i] = TcElem<T>::pack(e0, e1);
             pk[hf * 8 + 2 * i + 1] = TcElem<T>::pack(e2, e3);
           }
+        };
+        tmem_wait_ld();            // first 16 columns (requested before the fence above)
+        half_ds(0, sr0);
+        {
+          uint32_t sr1[16];
+          tmem_ld16(tlane + C::kColA + cg * 32 + 16, sr1);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // S^T(t+1) may overwrite dP^T(t)
+          half_ds(1, sr1);
         }
         // PD still holds P^T(t) until dV(t) has read it
         ok = mbar_wait(bar(FB_PT_FREE), t & 1, actx, 914);

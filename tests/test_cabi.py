@@ -50,3 +50,39 @@ def test_argument_validation_needs_no_gpu(built_lib):
     args = _C.PagedArgs()
     assert lib.fa_paged_decode(ctypes.byref(args), None) == -1
     assert lib.fa_paged_workspace_bytes(ctypes.byref(args)) == 0
+
+
+def test_one_pass_backward_and_cache_writer_validation_needs_no_gpu(built_lib):
+    """Workspace, stage and shape errors of the entries added beside the reference's launch pairs are
+    decided on the host, before any CUDA call."""
+    lib = _C.load()
+    lib.fa_flash_bwd_fused_workspace_bytes.restype = ctypes.c_int64
+    shape = _C.FlashShape(_C.FA_BF16, 2, 4, 2, 300, 500, 128, 1, 0.1)
+    # (B, H, ceil(M / 128) * 128, D) fp32
+    assert lib.fa_flash_bwd_fused_workspace_bytes(ctypes.byref(shape)) == 2 * 4 * 384 * 128 * 4
+    small = _C.FlashShape(_C.FA_BF16, 2, 4, 2, 300, 500, 32, 1, 0.1)       # head_dim 32: two-kernel path only
+    assert lib.fa_flash_bwd_fused_workspace_bytes(ctypes.byref(small)) == 0
+    drop = _C.FlashShape(_C.FA_BF16, 2, 4, 2, 300, 500, 128, 1, 0.1, 0.5, 1, 0)   # dropout: not covered
+    assert lib.fa_flash_bwd_fused_workspace_bytes(ctypes.byref(drop)) == 0
+    t = _C.Tensor4(0x1000, 0, 0, 128)
+    tensors = [ctypes.byref(t)] * 4
+    outs = [ctypes.byref(t)] * 3
+    f = ctypes.c_void_p(0x1000)
+    call = lambda ws, nbytes, stages: lib.fa_flash_bwd_fused_stages(
+        ctypes.byref(shape), *tensors, f, f, *outs, ws, ctypes.c_int64(nbytes), stages, None)
+    assert call(None, 1 << 30, 7) == -5                       # no workspace
+    assert call(ctypes.c_void_p(0x1000), 16, 7) == -5         # too small
+    assert call(ctypes.c_void_p(0x1004), 1 << 30, 7) == -5    # misaligned
+    assert call(ctypes.c_void_p(0x1000), 1 << 30, 0) == -1    # no stage selected
+    assert call(ctypes.c_void_p(0x1000), 1 << 30, 8) == -1
+    assert lib.fa_flash_bwd_fused(ctypes.byref(small), *tensors, f, f, *outs, ctypes.c_void_p(0x1000),
+                                  ctypes.c_int64(1 << 30), None) == -2
+    i64 = ctypes.c_int64
+    app = lambda dtype, head, key: lib.fa_paged_cache_append(
+        dtype, 4, 2, head, 16, key, f, i64(256), i64(128), f, f, i64(4096), i64(2048), i64(128), f, None)
+    assert app(7, 128, f) == -1                               # unknown dtype
+    assert app(_C.FA_F16, 12, f) == -2                        # head not a multiple of 8
+    assert app(_C.FA_F16, 128, None) == -1                    # missing pointer
+    assert app(_C.FA_F16, 128, ctypes.c_void_p(0x1008)) == -3 # misaligned
+    assert lib.fa_paged_cache_append(_C.FA_F16, 0, 2, 128, 16, None, None, i64(0), i64(0), None, None,
+                                     i64(0), i64(0), i64(0), None, None) == 0   # nothing to do

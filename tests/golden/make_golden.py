@@ -1,7 +1,7 @@
 """Generates tests/golden/*.pt by running the reference's own PyTorch oracles.
 
 Run once where the reference checkout is available:
-    python tests/golden/make_golden.py [/path/to/FlagAttention]
+    python tests/golden/make_golden.py /path/to/FlagAttention
 It imports src/flag_attn/testing/{flash,piecewise,paged}.py BY FILE PATH (the
 package itself needs triton kernels we do not want), runs them on CPU on small
 seeded inputs and stores inputs and outputs.  tests/test_oracle_golden.py then
@@ -16,7 +16,9 @@ import sys
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python %s /path/to/FlagAttention" % sys.argv[0])
+REF = sys.argv[1]
 
 
 def _load(name):

@@ -1,7 +1,7 @@
 """Generates tests/golden/philox.pt: dropout keep-masks made by the reference's own mask kernel.
 
 Run once where the reference checkout is available:
-    python tests/golden/make_philox_golden.py [/path/to/FlagAttention]
+    python tests/golden/make_philox_golden.py /path/to/FlagAttention
 The reference's recompute_mask_kernel (src/flag_attn/testing/dropout.py:5-16) is a triton
 kernel; it is loaded BY FILE PATH and run under triton's CPU interpreter (TRITON_INTERPRET=1),
 so no GPU is needed.  The raw `tl.rand(seed, offset, n_rounds=6)` numbers behind the masks are
@@ -20,7 +20,9 @@ import triton  # noqa: E402
 import triton.language as tl  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python %s /path/to/FlagAttention" % sys.argv[0])
+REF = sys.argv[1]
 
 
 @triton.jit

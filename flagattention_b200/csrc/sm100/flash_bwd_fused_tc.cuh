@@ -59,7 +59,7 @@ struct FusedBwdCfg {
 enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB_DO_FREE = 7,
                 FB_S_FULL = 9, FB_S_LOADED = 10, FB_DP_FULL = 11, FB_DP_LOADED = 12,
                 FB_PT_FULL = 13, FB_PT_FREE = 14, FB_DS_FULL = 15, FB_DS_FREE = 16,
-                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19, FB_LSE_FULL = 20, FB_DLT_FULL = 21 };
+                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19, FB_LSE_FULL = 20, FB_DLT_FULL = 21, FB_V_FULL = 22 };
 
 struct FusedBwdParams {
   BwdTcParams base;
@@ -81,8 +81,10 @@ __device__ __forceinline__ void bulk_commit() {
 __device__ __forceinline__ void bulk_wait_read_1() {
   asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
 }
-__device__ __forceinline__ void bulk_wait_all() {
-  asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+// waits until every group has finished reading its shared-memory source (what a CTA owes before
+// it gives its shared memory back; the additions themselves complete by the end of the grid)
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
 }
 // barrier among the four reduction warps (barrier 0 belongs to __syncthreads)
 __device__ __forceinline__ void red_warps_sync() {
@@ -146,7 +148,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(bar(FB_KV_FULL), 1);
+    mbar_init(bar(FB_KV_FULL), 1);   // K
+    mbar_init(bar(FB_V_FULL), 1);
     for (int s = 0; s < NQ; ++s) {
       mbar_init(bar(FB_Q_FULL + s), 1);
       mbar_init(bar(FB_Q_FREE + s), 1);
@@ -186,11 +189,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       tma_prefetch_desc(&map_do);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
-      mbar_expect_tx(bar(FB_KV_FULL), 2 * C::kTile);
-      for (int s = 0; s < KSUB; ++s) {
+      // K first and on a barrier of its own: S^T of the first tile needs K and Q only
+      mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
+      for (int s = 0; s < KSUB; ++s)
         tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, n0, hk, b);
-        tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_KV_FULL), s * 64, n0, hk, b);
-      }
       int issued_q = 0, issued_do = 0;
       bool ok = true;
       int sq = 0, phq = 1, sd = 0, phd = 1;   // slot and the "free" parity to wait for
@@ -204,6 +206,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
                       s * 64, m0, h, b);
         ++issued_q;
+        if (t == 0) {
+          mbar_expect_tx(bar(FB_V_FULL), C::kTile);
+          for (int s = 0; s < KSUB; ++s)
+            tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, n0, hk, b);
+        }
         ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 712);
         if (!ok) break;
         mbar_expect_tx(bar(FB_DO_FULL + sd), C::kTile);
@@ -262,6 +269,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         const uint32_t par = t & 1;
         // dP^T(t) = V dO^T over S^T(t), once every element-wise warp holds S^T(t) in registers
         ok = mbar_wait(bar(FB_S_LOADED), par, actx, 813);
+        if (ok && t == 0) ok = mbar_wait(bar(FB_V_FULL), 0, actx, 820);
         if (ok) ok = mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 814);
         if (!ok) break;
         tc_fence_after();
@@ -419,7 +427,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         buf ^= 1;
       }
     }
-    if (issuer) bulk_wait_all();   // shared memory must outlive the reads, the kernel the writes
+    if (issuer) bulk_wait_read_all();   // shared memory must outlive the copy engine's reads
   } else {
     // ------------------------------ element-wise warps --------------------------
     const int ew = warp - 2;

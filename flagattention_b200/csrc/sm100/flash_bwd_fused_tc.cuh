@@ -172,6 +172,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     mbar_init(bar(FB_LSE_FULL), 1);
     mbar_init(bar(FB_DLT_FULL), 1);
     fence_barrier_init();
+    // The loads of the first tile go out right here, before the TMEM allocation and the CTA-wide
+    // barrier below, so that their latency (the first bytes of K, V, Q, dO come from HBM) runs
+    // under the rest of the set-up.  K and Q first: S^T of the first tile needs only those.
+    if (T_tiles > 0) {
+      const int h0 = hk * G, m00 = mt_lo * BM;
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_v);
+      tma_prefetch_desc(&map_do);
+      mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, n0, hk, b);
+      mbar_expect_tx(bar(FB_Q_FULL), C::kTile);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kQ0 + s * BM * 128, &map_q, bar(FB_Q_FULL), s * 64, m00, h0, b);
+      mbar_expect_tx(bar(FB_V_FULL), C::kTile);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, n0, hk, b);
+      mbar_expect_tx(bar(FB_DO_FULL), C::kTile);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kDO0 + s * BM * 128, &map_do, bar(FB_DO_FULL), s * 64, m00, h0, b);
+    }
   }
   if (warp == 0) {
     tmem_alloc(smem + C::kMisc, C::kTmemCols);
@@ -185,39 +207,29 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   if (warp == 0) {
     // ------------------------------ producer -----------------------------------
     if (lane == 0 && T_tiles > 0) {
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_do);
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_v);
-      // K first and on a barrier of its own: S^T of the first tile needs K and Q only
-      mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
-      for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, n0, hk, b);
-      int issued_q = 0, issued_do = 0;
+      // (tile 0 was requested during set-up)
+      int issued_q = 1, issued_do = 1;
       bool ok = true;
       int sq = 0, phq = 1, sd = 0, phd = 1;   // slot and the "free" parity to wait for
       int h = hk * G, mt = mt_lo;
       for (int t = 0; t < T_tiles; ++t) {
         const int m0 = mt * BM;
-        ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 711);
-        if (!ok) break;
-        mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
-        for (int s = 0; s < KSUB; ++s)
-          tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
-                      s * 64, m0, h, b);
-        ++issued_q;
-        if (t == 0) {
-          mbar_expect_tx(bar(FB_V_FULL), C::kTile);
+        if (t > 0) {
+          ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 711);
+          if (!ok) break;
+          mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
           for (int s = 0; s < KSUB; ++s)
-            tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, n0, hk, b);
+            tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
+                        s * 64, m0, h, b);
+          ++issued_q;
+          ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 712);
+          if (!ok) break;
+          mbar_expect_tx(bar(FB_DO_FULL + sd), C::kTile);
+          for (int s = 0; s < KSUB; ++s)
+            tma_load_4d(smem + C::kDO0 + sd * C::kTile + s * BM * 128, &map_do, bar(FB_DO_FULL + sd),
+                        s * 64, m0, h, b);
+          ++issued_do;
         }
-        ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 712);
-        if (!ok) break;
-        mbar_expect_tx(bar(FB_DO_FULL + sd), C::kTile);
-        for (int s = 0; s < KSUB; ++s)
-          tma_load_4d(smem + C::kDO0 + sd * C::kTile + s * BM * 128, &map_do, bar(FB_DO_FULL + sd),
-                      s * 64, m0, h, b);
-        ++issued_do;
         if (++sq == NQ) sq = 0, phq ^= 1;
         if (++sd == NDO) sd = 0, phd ^= 1;
         if (++mt == mt_hi) mt = mt_lo, ++h;

@@ -401,6 +401,54 @@ def run_decode(args, dist, rank, world, device):
                 gpu_launches=2 * steps)
 
 
+def run_rotary(args, dist, rank, world, device):
+    """rotary_pair on q at the piecewise workload's shape (B=1, H=48, L=16384, D=128, bf16): one read
+    of x, two rotated copies written; forward and backward timed separately, device-resident."""
+    import flagattention_b200 as fa
+    B, H, L, D = 1, 48, 16384, 128
+    gen = torch.Generator(device=device).manual_seed(10086 + 7 + rank)
+    x = torch.randn((B, H, L, D), generator=gen, device=device).to(torch.bfloat16).requires_grad_()
+    g1, g2 = torch.randn_like(x), torch.randn_like(x)
+    c1, s1 = fa.rotary_tables(L, D, device=device)
+    c2, s2 = fa.rotary_tables(L, D, position_scale=0.25, device=device)
+    # a 192 MiB tensor read and two written per call: larger than L2 by itself
+    steps = max(args.steps, 10)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+
+    def run(n, timed):
+        if timed:
+            ev[0].record()
+        outs = None
+        for _ in range(n):
+            outs = fa.rotary_pair(x, c1, s1, c2, s2)
+        if timed:
+            ev[1].record()
+        for _ in range(n):
+            torch.autograd.grad(outs, (x,), (g1, g2), retain_graph=True)
+        if timed:
+            ev[2].record()
+
+    run(max(3, args.warmup), False)
+    barrier(dist)
+    run(steps, True)
+    torch.cuda.synchronize()
+    barrier(dist)
+    ms_f = max_over_ranks(dist, ev[0].elapsed_time(ev[1]), device) / steps
+    ms_b = max_over_ranks(dist, ev[1].elapsed_time(ev[2]), device) / steps
+    algo_bytes = 3 * x.numel() * 2
+    peaks = load_peaks()
+    gbs_f, gbs_b = algo_bytes / (ms_f * 1e-3) / 1e9, algo_bytes / (ms_b * 1e-3) / 1e9
+    return dict(metric="rotary_pair HBM GB/s", value=round(world * gbs_f, 1), unit="GB/s",
+                ms_fwd=round(ms_f, 4), ms_bwd=round(ms_b, 4), bwd_gbs=round(world * gbs_b, 1),
+                algorithmic_bytes=algo_bytes,
+                config=dict(workload="rotary_pair bf16, two embeddings of one tensor", B=B, H=H, L=L, D=D,
+                            l2="each tensor (192 MiB) is larger than L2"),
+                roofline=dict(bound="hbm", kernel="rotary_pair_fwd_kernel", achieved=round(gbs_f, 1),
+                              peak=peaks["hbm_gbs"], unit="GB/s", frac=round(gbs_f / peaks["hbm_gbs"], 4),
+                              peak_source=peaks["source"], traffic=None),
+                gpu_launches=2 * steps)
+
+
 def run_paged(args, dist, rank, world, device):
     import flagattention_b200 as fa
     c = PAGED_CFG
@@ -555,6 +603,7 @@ def main():
     paged = None if (args.skip_paged or args.only == "flash") else run_paged(args, dist, rank, world, device)
     pw = None if (args.skip_piecewise or args.only == "flash") else run_piecewise(args, dist, rank, world, device)
     dec = None if (args.skip_paged or args.only == "flash") else run_decode(args, dist, rank, world, device)
+    rot = None if (args.skip_piecewise or args.only == "flash") else run_rotary(args, dist, rank, world, device)
     cpu = None
     if rank == 0 and not args.skip_cpu and world == 1:
         cpu, _ = cpu_flash_sample(2)
@@ -572,7 +621,7 @@ def main():
                        "l2": "inputs (4 x 128 MiB) are larger than the 126 MB L2"},
             "roofline": fl["roofline"], "cpu_baseline": cpu, "e2e": fl["e2e"],
             "gpu_launches": fl["launches"], "clocks": fl["clocks"], "paged": paged,
-            "piecewise": pw, "decode": dec,
+            "piecewise": pw, "decode": dec, "rotary": rot,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = (
     "fa_paged_decode", "fa_paged_reduce", "fa_paged_workspace_bytes", "fa_paged_trace_blocks",
     "fa_paged_attention_noalloc", "fa_dropout_mask",
     "fa_flash_bwd_fused", "fa_flash_bwd_fused_stages", "fa_flash_bwd_fused_workspace_bytes", "fa_piecewise_bwd_fused",
-    "fa_paged_cache_append",
+    "fa_paged_cache_append", "fa_rotary_pair_fwd", "fa_rotary_pair_bwd",
     "fa_device_status", "fa_status_string", "fa_version",
 )
 

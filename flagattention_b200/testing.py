@@ -13,7 +13,7 @@ import torch
 
 from .dropout import recompute_mask  # noqa: F401
 
-__all__ = ["flash_attention", "piecewise_attention", "paged_attention", "recompute_mask"]
+__all__ = ["flash_attention", "piecewise_attention", "paged_attention", "recompute_mask", "rotary_pair"]
 
 
 def _causal_mask(m, n, device):
@@ -76,3 +76,26 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, s
         p = torch.softmax(torch.bmm(qq, kk.transpose(1, 2)) * scale, dim=-1)
         out[i] = torch.bmm(p, vv).reshape(-1, head).to(out.dtype)
     return out
+
+
+def rotary_pair(x, cos1, sin1, cos2, sin2, positions=None, interleaved=False, upcast=True):
+    """PyTorch reference of flagattention_b200.rotary_pair, differentiable through autograd.
+    upcast=False does the arithmetic in x's own dtype (the same-precision comparison)."""
+    half = x.shape[-1] // 2
+    if positions is None:
+        positions = torch.arange(x.shape[2], device=x.device)
+    positions = positions.to(device=x.device, dtype=torch.int64)
+    if positions.dim() == 1:
+        positions = positions[None]
+    work = x.float() if upcast else x
+    lo, hi = (work[..., 0::2], work[..., 1::2]) if interleaved else (work[..., :half], work[..., half:])
+
+    def one(cos, sin):
+        rows = positions.clamp(0, cos.shape[0] - 1)
+        c = cos.to(work.device)[rows][:, None, :, :half].to(work.dtype)
+        s = sin.to(work.device)[rows][:, None, :, :half].to(work.dtype)
+        ylo, yhi = lo * c - hi * s, hi * c + lo * s
+        y = torch.stack((ylo, yhi), dim=-1).flatten(-2) if interleaved else torch.cat((ylo, yhi), dim=-1)
+        return y.to(x.dtype)
+
+    return one(cos1, sin1), one(cos2, sin2)

@@ -287,7 +287,40 @@ int fa_paged_trace_blocks(const fa_paged_args *a, int64_t *visited, int32_t max_
                           void *stream);
 
 /* ---------------------------------------------------------------------- */
-/* Health check of the tensor-core kernels.  Every wait inside them is bounded
+/* Producer of piecewise_attention's operands                               */
+/* ---------------------------------------------------------------------- */
+
+/* Two rotary position embeddings of one (B, H, L, D) tensor in one pass:
+ *   out_e = rotate(x; cos_e, sin_e),  e = 1, 2,
+ * where, for rotation pair i of the row at position p (column i of row p of the tables),
+ *   lo' = lo * cos[p, i] - hi * sin[p, i],   hi' = hi * cos[p, i] + lo * sin[p, i],
+ * and the pair is (x[i], x[i + D/2]) (interleaved = 0) or (x[2i], x[2i + 1]) (interleaved = 1).
+ * Tables: fp32, `table_rows` rows of D/2 used columns, `table_stride` elements between rows
+ * (a multiple of 4), 16-byte aligned.  positions: int64 (B, L) with row stride pos_stride_b
+ * (0 broadcasts one row over the batch), or NULL for p = l; a position outside the tables is
+ * clamped to the nearest row.  D a multiple of 16, at most 512; tensors as everywhere (unit
+ * inner stride, 16-byte aligned rows).  Every product and sum is rounded to fp32 on its own
+ * (no fused multiply-add) and the result rounded once to the 16-bit type, so the output is
+ * bit-identical to the plain fp32 expression above.
+ * The reference has no such kernel: its README describes the caller's step in prose (two
+ * position embeddings applied to q and k, giving q1, q2 and k1, k2: README.md:136-138) and its
+ * operator takes the four results (src/flag_attn/piecewise.py:169-191). */
+int fa_rotary_pair_fwd(int32_t dtype, int32_t B, int32_t H, int32_t L, int32_t D,
+                       int32_t interleaved, const fa_tensor4 *x, const float *cos1,
+                       const float *sin1, const float *cos2, const float *sin2,
+                       int64_t table_stride, int32_t table_rows, const int64_t *positions,
+                       int64_t pos_stride_b, const fa_tensor4 *out1, const fa_tensor4 *out2,
+                       void *stream);
+/* Its backward: dx = R1^T g1 + R2^T g2 (the rotations by the opposite angles, summed in fp32 in
+ * that order, rounded once). */
+int fa_rotary_pair_bwd(int32_t dtype, int32_t B, int32_t H, int32_t L, int32_t D,
+                       int32_t interleaved, const fa_tensor4 *g1, const fa_tensor4 *g2,
+                       const float *cos1, const float *sin1, const float *cos2, const float *sin2,
+                       int64_t table_stride, int32_t table_rows, const int64_t *positions,
+                       int64_t pos_stride_b, const fa_tensor4 *dx, void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* Health check of the tensor-core kernels. Every wait inside them is bounded
  * (about a second); a wait that runs out stores a code naming the wait in a
  * per-device status word, and the kernel tears down and returns instead of
  * hanging.  This call synchronises with the device, copies the word to *out

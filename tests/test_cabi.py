@@ -86,3 +86,24 @@ def test_one_pass_backward_and_cache_writer_validation_needs_no_gpu(built_lib):
     assert app(_C.FA_F16, 128, ctypes.c_void_p(0x1008)) == -3 # misaligned
     assert lib.fa_paged_cache_append(_C.FA_F16, 0, 2, 128, 16, None, None, i64(0), i64(0), None, None,
                                      i64(0), i64(0), i64(0), None, None) == 0   # nothing to do
+
+
+def test_rotary_pair_validation_needs_no_gpu(built_lib):
+    lib = _C.load()
+    i64 = ctypes.c_int64
+    t = _C.Tensor4(0x1000, 0, 128 * 64, 64)
+    f = ctypes.c_void_p(0x1000)
+
+    def fwd(dtype=_C.FA_BF16, D=64, table=f, stride=32, x=t, rows=10):
+        return lib.fa_rotary_pair_fwd(dtype, 1, 2, 128, D, 0, ctypes.byref(x), table, f, f, f, i64(stride),
+                                      rows, None, i64(0), ctypes.byref(t), ctypes.byref(t), None)
+    assert fwd(dtype=5) == -1
+    assert fwd(D=24) == -2 and fwd(D=1024) == -2              # head_dim rule
+    assert fwd(table=None) == -1 and fwd(rows=0) == -1
+    assert fwd(stride=16) == -3 and fwd(stride=34) == -3      # rows shorter than D / 2; odd stride
+    assert fwd(table=ctypes.c_void_p(0x1004)) == -3
+    assert fwd(x=_C.Tensor4(0x1002, 0, 128 * 64, 64)) == -3
+    assert lib.fa_rotary_pair_bwd(_C.FA_F16, 0, 2, 128, 64, 1, None, None, f, f, f, f, i64(32), 10, None,
+                                  i64(0), None, None) == 0    # empty batch: nothing to do
+    assert lib.fa_rotary_pair_bwd(_C.FA_F16, 1, 2, 128, 64, 1, None, ctypes.byref(t), f, f, f, f, i64(32),
+                                  10, None, i64(0), ctypes.byref(t), None) == -1

@@ -121,3 +121,27 @@ def test_dropout_mask_matches_reference_kernel():
     for c in _philox_golden()["masks"]:
         mine = dropout_mask(c["B"], c["H"], c["M"], c["N"], c["p"], c["seed"], c["offset"])
         assert np.array_equal(mine, c["mask"].numpy())
+
+
+def test_rotary_oracle_matches_the_transformers_package():
+    """The reference has no code for the rotary step that produces piecewise_attention's operands, so
+    the oracle's formula is held to an independent implementation instead: llama's
+    apply_rotary_pos_emb of the `transformers` package (half-split pairs), when importable."""
+    llama = pytest.importorskip("transformers.models.llama.modeling_llama")
+    import flagattention_b200 as fa
+    gen = torch.Generator().manual_seed(11)
+    q = torch.randn((2, 3, 40, 64), generator=gen)
+    k = torch.randn((2, 3, 40, 64), generator=gen)
+    cos, sin = fa.rotary_tables(100, 64)
+    pos = torch.randint(0, 100, (2, 40), generator=gen)
+    qe, ke = llama.apply_rotary_pos_emb(q, k, torch.cat((cos, cos), -1)[pos], torch.cat((sin, sin), -1)[pos])
+    assert torch.equal(oracle.rotary(q, cos, sin, pos), qe)
+    assert torch.equal(oracle.rotary(k, cos, sin, pos), ke)
+    # the interleaved layout is the same rotation on a permuted head dimension
+    perm = torch.stack((torch.arange(32), torch.arange(32) + 32), -1).flatten()
+    assert torch.equal(oracle.rotary(q[..., perm], cos, sin, pos, interleaved=True), qe[..., perm])
+    # the backward is the transpose: <R x, g> == <x, R^T g>
+    g = torch.randn((2, 3, 40, 64), generator=gen)
+    dx = oracle.rotary_pair_backward(g, g, cos, sin, cos, sin, pos)
+    lhs = (oracle.rotary(q, cos, sin, pos) * g).sum() * 2
+    assert abs(lhs.item() - (q * dx).sum().item()) < 1e-2

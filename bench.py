@@ -402,16 +402,17 @@ def run_decode(args, dist, rank, world, device):
 
 
 def run_rotary(args, dist, rank, world, device):
-    """rotary_pair on q at the piecewise workload's shape (B=1, H=48, L=16384, D=128, bf16): one read
-    of x, two rotated copies written; forward and backward timed separately, device-resident."""
+    """rotary_pair on q and k of the piecewise workload stacked along the batch (B=2, H=48, L=16384,
+    D=128, bf16): one read of x, two rotated copies written; forward and backward timed separately,
+    device-resident."""
     import flagattention_b200 as fa
-    B, H, L, D = 1, 48, 16384, 128
+    B, H, L, D = 2, 48, 16384, 128
     gen = torch.Generator(device=device).manual_seed(10086 + 7 + rank)
     x = torch.randn((B, H, L, D), generator=gen, device=device).to(torch.bfloat16).requires_grad_()
     g1, g2 = torch.randn_like(x), torch.randn_like(x)
     c1, s1 = fa.rotary_tables(L, D, device=device)
     c2, s2 = fa.rotary_tables(L, D, position_scale=0.25, device=device)
-    # a 192 MiB tensor read and two written per call: larger than L2 by itself
+    # a 384 MiB tensor read and two written per call: larger than L2 by itself
     steps = max(args.steps, 10)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
 
@@ -442,7 +443,7 @@ def run_rotary(args, dist, rank, world, device):
                 ms_fwd=round(ms_f, 4), ms_bwd=round(ms_b, 4), bwd_gbs=round(world * gbs_b, 1),
                 algorithmic_bytes=algo_bytes,
                 config=dict(workload="rotary_pair bf16, two embeddings of one tensor", B=B, H=H, L=L, D=D,
-                            l2="each tensor (192 MiB) is larger than L2"),
+                            l2="each tensor (384 MiB) is larger than L2"),
                 roofline=dict(bound="hbm", kernel="rotary_pair_fwd_kernel", achieved=round(gbs_f, 1),
                               peak=peaks["hbm_gbs"], unit="GB/s", frac=round(gbs_f / peaks["hbm_gbs"], 4),
                               peak_source=peaks["source"], traffic=None),

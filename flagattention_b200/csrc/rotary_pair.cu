@@ -28,7 +28,7 @@ struct RotaryTables {
   int rows;
 };
 
-constexpr int kRotaryThreads = 256;
+constexpr int kRotaryThreads = 128;   // five CTAs per SM at the kernels' register count
 
 struct RotaryCoef {
   float c1[8], s1[8], c2[8], s2[8];
@@ -124,9 +124,9 @@ __device__ __forceinline__ bool rotary_setup(RotaryWork &w, RotaryCoef &co, cons
 }
 
 template <typename T, bool INTERLEAVED>
-__global__ void __launch_bounds__(kRotaryThreads)
-    rotary_pair_fwd_kernel(const T *__restrict__ x, Strides sx, T *out1, Strides s1, T *out2,
-                           Strides s2, RotaryTables t, const int64_t *__restrict__ positions,
+__global__ void __launch_bounds__(kRotaryThreads, 5)
+    rotary_pair_fwd_kernel(const T *__restrict__ x, Strides sx, T *__restrict__ out1, Strides s1,
+                           T *__restrict__ out2, Strides s2, RotaryTables t, const int64_t *__restrict__ positions,
                            int64_t pos_stride_b, int H, int L, int D, int heads_per_cta) {
   RotaryWork w;
   RotaryCoef co;
@@ -161,9 +161,9 @@ __global__ void __launch_bounds__(kRotaryThreads)
 
 // dx = R1^T g1 + R2^T g2; the transpose of a rotation is the rotation by the opposite angle.
 template <typename T, bool INTERLEAVED>
-__global__ void __launch_bounds__(kRotaryThreads)
+__global__ void __launch_bounds__(kRotaryThreads, 5)
     rotary_pair_bwd_kernel(const T *__restrict__ g1, Strides s1, const T *__restrict__ g2,
-                           Strides s2, T *dx, Strides sx, RotaryTables t,
+                           Strides s2, T *__restrict__ dx, Strides sx, RotaryTables t,
                            const int64_t *__restrict__ positions, int64_t pos_stride_b, int H, int L,
                            int D, int heads_per_cta) {
   RotaryWork w;
@@ -203,12 +203,14 @@ struct RotaryLaunch {
   int heads_per_cta;
 };
 
-// Rows of one CTA share nothing, so the heads are split over grid.z until the grid fills the
-// machine a few times over (short sequences would otherwise leave most SMs idle).
+// Rows of one CTA share nothing, so the heads are split over grid.z until the grid is some twenty
+// waves of resident CTAs deep: short sequences then still fill the machine, and long ones end
+// without a long under-filled last wave.  A CTA keeps at least a few heads where it can, since
+// its threads fetch their table values once per CTA.
 RotaryLaunch plan(int B, int H, int L, int D) {
   const int rows = kRotaryThreads / (D / 16);
   const int gx = (L + rows - 1) / rows;
-  const int64_t want = 148 * 4;
+  const int64_t want = 148 * 5 * 20;
   int z = (int)((want + (int64_t)gx * B - 1) / ((int64_t)gx * B));
   z = z < 1 ? 1 : (z > H ? H : z);
   const int hpc = (H + z - 1) / z;

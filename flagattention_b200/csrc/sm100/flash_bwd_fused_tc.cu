@@ -36,11 +36,13 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
                         const fa_tensor4 *dv, float *workspace, cudaStream_t stream, int mode = 0,
                         int w = 0, int dv_accumulate = 0, int stages = 7) {
   using C = FusedBwdCfg<D>;
-  CUtensorMap mq, mdo, mk, mv;
+  CUtensorMap mq, mdo, mk, mv, mdk, mdv;
   if (!make_map_bhld(&mq, q, s->dtype, s->B, s->H, s->M, D, C::BM) ||
       !make_map_bhld(&mdo, d_o, s->dtype, s->B, s->H, s->M, D, C::BM) ||
       !make_map_bhld(&mk, k, s->dtype, s->B, s->Hk, s->N, D, C::BN) ||
-      !make_map_bhld(&mv, v, s->dtype, s->B, s->Hk, s->N, D, C::BN))
+      !make_map_bhld(&mv, v, s->dtype, s->B, s->Hk, s->N, D, C::BN) ||
+      !make_map_bhld(&mdk, dk, s->dtype, s->B, s->Hk, s->N, D, C::BN) ||
+      !make_map_bhld(&mdv, dv, s->dtype, s->B, s->Hk, s->N, D, C::BN))
     return FA_ERR_UNSUPPORTED;
   auto kern = flash_bwd_fused_tc_kernel<T, D>;
   static unsigned long long done = 0;
@@ -61,7 +63,7 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
     return FA_ERR_LAUNCH;
   if (stages & 2) {
     dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
-    kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, fp);
+    kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, mdk, mdv, fp);
     FA_CHECK_LAUNCH();
   }
   if (stages & 4) {

@@ -104,6 +104,31 @@ __device__ __forceinline__ bool red_warps_all(bool ok) {
   return out != 0;
 }
 
+// barrier 2 with a vote: the 16 element-wise warps (512 threads)
+__device__ __forceinline__ bool ew_warps_all(bool ok) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 2, 512, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}\n"
+      : "=r"(out)
+      : "r"((uint32_t)ok)
+      : "memory");
+  return out != 0;
+}
+
+// one box of a (d, l, h, b) tensor map, shared memory -> global memory; rows past the tensor's
+// end are dropped by the copy engine
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t smem_src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n"
+      :
+      : "l"(map), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 // warps: 0 TMA producer, 1 MMA issuer, 2..17 element-wise, 18..21 dQ reduction (one per TMEM
 // lane slice), 22 statistics
 constexpr int kFusedThreads = kBwdThreads + 5 * 32;   // 736
@@ -113,7 +138,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     flash_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                               const __grid_constant__ CUtensorMap map_do,
                               const __grid_constant__ CUtensorMap map_k,
-                              const __grid_constant__ CUtensorMap map_v, const FusedBwdParams fp) {
+                              const __grid_constant__ CUtensorMap map_v,
+                              const __grid_constant__ CUtensorMap map_dk,
+                              const __grid_constant__ CUtensorMap map_dv, const FusedBwdParams fp) {
   using C = FusedBwdCfg<D>;
   constexpr int BM = C::BM, BN = C::BN, KSUB = C::KSUB, NQ = C::NQ, NDO = C::NDO;
   const BwdTcParams &p = fp.base;
@@ -181,6 +208,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_v);
       tma_prefetch_desc(&map_do);
+      tma_prefetch_desc(&map_dk);
+      tma_prefetch_desc(&map_dv);
       mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
         tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, n0, hk, b);
@@ -587,45 +616,98 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       if (lane == 0) mbar_arrive(bar(FB_DS_FULL));
     }
 
-    if (ok && T_tiles > 0) {
-      ok = mbar_wait(bar(FB_DONE), 0, actx, 916);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
-      // warps of column groups 0 / 1 store dK, groups 2 / 3 store dV; each thread half a row
-      const int which = cg >> 1, half = cg & 1;
-      constexpr int COLS = D / 2;
-      T *orow = which == 0 ? row_ptr_mut<T>(p.dk, p.sdk, b, hk, key)
-                           : row_ptr_mut<T>(p.dv, p.sdv, b, hk, key);
-      const float scale = which == 0 ? p.sm_scale : 1.f;
-      const uint32_t col_base = which == 0 ? C::kColDK : C::kColDV;
+    // ---- write-out of dV and dK: warp (slice, cg) owns columns cg * D / 4 .. of its 32 rows ----
+    // dV is final once its last product has been committed (the PT_FREE wait that ended the loop),
+    // so it is converted and handed to the copy engine while dQ and dK of the last tile still run
+    // on the tensor cores; dK follows after the last commit.  The tiles are staged in the shared
+    // memory of V and K (both dead by then) in the layout of their own loads, and leave as bulk
+    // tensor stores, which also drop the rows past N.  Two cases keep per-thread global stores:
+    // a dV that is added to (the second launch of a piecewise backward) and a CTA without tiles.
+    constexpr int QC = D / 4;
+    const int col0 = cg * QC;
+    auto load_cols = [&](uint32_t col_base, uint32_t (&ov)[QC]) {
+      if (QC == 32) tmem_ld32(tlane + col_base + col0, *reinterpret_cast<uint32_t(*)[32]>(ov));
+      else tmem_ld16(tlane + col_base + col0, ov);
+      tmem_wait_ld();
+    };
+    auto pack8 = [&](const uint32_t *ov, float scale) {
+      return make_uint4(
+          TcElem<T>::pack(__uint_as_float(ov[0]) * scale, __uint_as_float(ov[1]) * scale),
+          TcElem<T>::pack(__uint_as_float(ov[2]) * scale, __uint_as_float(ov[3]) * scale),
+          TcElem<T>::pack(__uint_as_float(ov[4]) * scale, __uint_as_float(ov[5]) * scale),
+          TcElem<T>::pack(__uint_as_float(ov[6]) * scale, __uint_as_float(ov[7]) * scale));
+    };
+    auto stage = [&](int region, const uint32_t (&ov)[QC], float scale) {
+      uint8_t *base = smem_gen + region + (col0 / 64) * (128 * 128) + row * 128;
+      const int ch0 = (col0 % 64) / 8;
 #pragma unroll
-      for (int c = 0; c < COLS / 32; ++c) {
-        uint32_t ov[32];
-        const int col0 = half * COLS + c * 32;
-        if (T_tiles > 0) {
-          tmem_ld32(tlane + col_base + col0, ov);
-          tmem_wait_ld();
-        } else {
+      for (int j = 0; j < QC / 8; ++j)
+        *reinterpret_cast<uint4 *>(base + (((ch0 + j) ^ (row & 7)) << 4)) = pack8(ov + 8 * j, scale);
+    };
+    auto direct = [&](void *out, const Strides &so, uint32_t (&ov)[QC], float scale, bool add) {
+      if (!key_ok) return;
+      T *orow = row_ptr_mut<T>(out, so, b, hk, key) + col0;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = 0u;
-        }
-        if (which == 1 && p.dv_accumulate && key_ok) {
+      for (int j = 0; j < QC / 8; ++j) {
+        if (add) {
+          const uint4 old = *reinterpret_cast<const uint4 *>(orow + j * 8);
+          const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint4 old = *reinterpret_cast<const uint4 *>(orow + col0 + i * 8);
-            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-            for (int e2 = 0; e2 < 4; ++e2) {
-              const float2 f = TcElem<T>::unpack(ow[e2]);
-              ov[8 * i + 2 * e2] = __float_as_uint(__uint_as_float(ov[8 * i + 2 * e2]) + f.x);
-              ov[8 * i + 2 * e2 + 1] = __float_as_uint(__uint_as_float(ov[8 * i + 2 * e2 + 1]) + f.y);
-            }
+          for (int e2 = 0; e2 < 4; ++e2) {
+            const float2 f = TcElem<T>::unpack(ow[e2]);
+            ov[8 * j + 2 * e2] = __float_as_uint(__uint_as_float(ov[8 * j + 2 * e2]) + f.x);
+            ov[8 * j + 2 * e2 + 1] = __float_as_uint(__uint_as_float(ov[8 * j + 2 * e2 + 1]) + f.y);
           }
         }
-        if (key_ok) store_row32<T>(orow + col0, ov, scale);
+        *reinterpret_cast<uint4 *>(orow + j * 8) = pack8(ov + 8 * j, scale);
       }
+    };
+    const bool elected = ew == 0 && lane == 0;
+    if (T_tiles > 0) {
+      // every element-wise warp runs both votes below, whatever happened to its own waits
+      uint32_t ov[QC];
+      const bool bulk_dv = !p.dv_accumulate;
+      if (ok) {
+        tc_fence_after();
+        load_cols(C::kColDV, ov);
+        if (bulk_dv) {
+          stage(C::kV, ov, 1.f);
+          fence_proxy_async_smem();
+        } else {
+          direct(p.dv, p.sdv, ov, 1.f, true);
+        }
+      }
+      ok = ew_warps_all(ok);
+      if (ok && bulk_dv && elected) {
+#pragma unroll
+        for (int s = 0; s < KSUB; ++s)
+          tma_store_4d(&map_dv, smem + C::kV + s * BN * 128, s * 64, n0, hk, b);
+        bulk_commit();
+      }
+      if (ok) ok = mbar_wait(bar(FB_DONE), 0, actx, 916);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        load_cols(C::kColDK, ov);
+        stage(C::kK, ov, p.sm_scale);
+        fence_proxy_async_smem();
+      }
+      ok = ew_warps_all(ok);
+      if (elected) {
+        if (ok) {
+#pragma unroll
+          for (int s = 0; s < KSUB; ++s)
+            tma_store_4d(&map_dk, smem + C::kK + s * BN * 128, s * 64, n0, hk, b);
+          bulk_commit();
+        }
+        bulk_wait_read_all();   // shared memory must outlive the copy engine's reads
+      }
+    } else if (ok) {
+      uint32_t ov[QC];
+#pragma unroll
+      for (int i = 0; i < QC; ++i) ov[i] = 0u;
+      direct(p.dk, p.sdk, ov, 1.f, false);
+      if (!p.dv_accumulate) direct(p.dv, p.sdv, ov, 1.f, false);
     }
   }
 

@@ -572,7 +572,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling)")
     ap.add_argument("--skip-piecewise", action="store_true")
-    ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise"],
+    ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise", "rotary"],
                     help="run one workload only (profiling); the JSON line is then partial")
     ap.add_argument("--paged-seqs", type=int, default=PAGED_CFG["num_seqs"],
                     help="number of sequences of the paged workload (smaller for profiler captures)")
@@ -594,6 +594,11 @@ def main():
         paged = run_paged(args, dist, rank, world, device)
         if rank == 0:
             print(json.dumps({"partial": True, "paged": paged}), flush=True)
+        return
+    if args.only == "rotary":
+        rot = run_rotary(args, dist, rank, world, device)
+        if rank == 0:
+            print(json.dumps({"partial": True, "rotary": rot}), flush=True)
         return
     if args.only == "piecewise":
         pw = run_piecewise(args, dist, rank, world, device)

@@ -28,7 +28,7 @@ struct RotaryTables {
   int rows;
 };
 
-constexpr int kRotaryThreads = 128;   // five CTAs per SM at the kernels' register count
+constexpr int kRotaryThreads = 128;   // four CTAs per SM at the kernels' register count
 
 struct RotaryCoef {
   float c1[8], s1[8], c2[8], s2[8];
@@ -101,13 +101,18 @@ struct RotaryWork {
 
 template <bool INTERLEAVED>
 __device__ __forceinline__ bool rotary_setup(RotaryWork &w, RotaryCoef &co, const RotaryTables &t,
-                                             const int64_t *positions, int64_t pos_stride_b, int H,
-                                             int L, int D, int heads_per_cta) {
+                                             const int64_t *positions, int64_t pos_stride_b, int B,
+                                             int H, int L, int D, int heads_per_cta) {
   const int tpr = D / 16, rows = kRotaryThreads / tpr;
   const int r = threadIdx.x / tpr, j = threadIdx.x - r * tpr;
-  w.l = blockIdx.x * rows + r;
-  w.b = blockIdx.y;
-  w.h_lo = blockIdx.z * heads_per_cta;
+  // CTA order: head chunk fastest, then batch, then row block, so that the CTAs that read the same
+  // table rows run at the same time and the rows are fetched from DRAM once
+  const int Z = (H + heads_per_cta - 1) / heads_per_cta;
+  const unsigned bx = blockIdx.x;
+  const int hz = bx % Z;
+  w.b = (bx / Z) % B;
+  w.l = (int)(bx / ((unsigned)Z * B)) * rows + r;
+  w.h_lo = hz * heads_per_cta;
   w.h_hi = min(H, w.h_lo + heads_per_cta);
   if (r >= rows || w.l >= L) return false;
   w.off_a = INTERLEAVED ? 16 * j : 8 * j;
@@ -124,14 +129,15 @@ __device__ __forceinline__ bool rotary_setup(RotaryWork &w, RotaryCoef &co, cons
 }
 
 template <typename T, bool INTERLEAVED>
-__global__ void __launch_bounds__(kRotaryThreads, 5)
+__global__ void __launch_bounds__(kRotaryThreads, 4)
     rotary_pair_fwd_kernel(const T *__restrict__ x, Strides sx, T *__restrict__ out1, Strides s1,
                            T *__restrict__ out2, Strides s2, RotaryTables t, const int64_t *__restrict__ positions,
-                           int64_t pos_stride_b, int H, int L, int D, int heads_per_cta) {
+                           int64_t pos_stride_b, int B, int H, int L, int D, int heads_per_cta) {
   RotaryWork w;
   RotaryCoef co;
-  if (!rotary_setup<INTERLEAVED>(w, co, t, positions, pos_stride_b, H, L, D, heads_per_cta)) return;
-#pragma unroll 2
+  if (!rotary_setup<INTERLEAVED>(w, co, t, positions, pos_stride_b, B, H, L, D, heads_per_cta))
+    return;
+#pragma unroll 4
   for (int h = w.h_lo; h < w.h_hi; ++h) {
     const T *src = x + w.b * sx.b + h * sx.h + w.l * sx.l;
     float a[8], b[8], lo[8], hi[8], ylo[8], yhi[8];
@@ -161,15 +167,16 @@ __global__ void __launch_bounds__(kRotaryThreads, 5)
 
 // dx = R1^T g1 + R2^T g2; the transpose of a rotation is the rotation by the opposite angle.
 template <typename T, bool INTERLEAVED>
-__global__ void __launch_bounds__(kRotaryThreads, 5)
+__global__ void __launch_bounds__(kRotaryThreads, 4)
     rotary_pair_bwd_kernel(const T *__restrict__ g1, Strides s1, const T *__restrict__ g2,
                            Strides s2, T *__restrict__ dx, Strides sx, RotaryTables t,
-                           const int64_t *__restrict__ positions, int64_t pos_stride_b, int H, int L,
-                           int D, int heads_per_cta) {
+                           const int64_t *__restrict__ positions, int64_t pos_stride_b, int B, int H,
+                           int L, int D, int heads_per_cta) {
   RotaryWork w;
   RotaryCoef co;
-  if (!rotary_setup<INTERLEAVED>(w, co, t, positions, pos_stride_b, H, L, D, heads_per_cta)) return;
-#pragma unroll 2
+  if (!rotary_setup<INTERLEAVED>(w, co, t, positions, pos_stride_b, B, H, L, D, heads_per_cta))
+    return;
+#pragma unroll 4
   for (int h = w.h_lo; h < w.h_hi; ++h) {
     const T *p1 = g1 + w.b * s1.b + h * s1.h + w.l * s1.l;
     const T *p2 = g2 + w.b * s2.b + h * s2.h + w.l * s2.l;
@@ -210,12 +217,12 @@ struct RotaryLaunch {
 RotaryLaunch plan(int B, int H, int L, int D) {
   const int rows = kRotaryThreads / (D / 16);
   const int gx = (L + rows - 1) / rows;
-  const int64_t want = 148 * 5 * 20;
+  const int64_t want = 148 * 4 * 20;
   int z = (int)((want + (int64_t)gx * B - 1) / ((int64_t)gx * B));
   z = z < 1 ? 1 : (z > H ? H : z);
   const int hpc = (H + z - 1) / z;
   z = (H + hpc - 1) / hpc;
-  return {dim3(gx, B, z), hpc};
+  return {dim3((unsigned)((int64_t)gx * B * z)), hpc};
 }
 
 int check_common(int32_t dtype, int32_t B, int32_t H, int32_t L, int32_t D, const float *cos1,
@@ -228,7 +235,7 @@ int check_common(int32_t dtype, int32_t B, int32_t H, int32_t L, int32_t D, cons
   if (table_stride < D / 2 || table_stride % 4) return FA_ERR_ALIGNMENT;
   if (!aligned16(cos1) || !aligned16(sin1) || !aligned16(cos2) || !aligned16(sin2))
     return FA_ERR_ALIGNMENT;
-  if (B > 65535) return FA_ERR_TOO_LARGE;
+  if ((int64_t)B * H * ((L + 1) / 2 + 1) >= (1ll << 31)) return FA_ERR_TOO_LARGE;   // one-dimensional grid
   return FA_OK;
 }
 
@@ -254,7 +261,7 @@ extern "C" int fa_rotary_pair_fwd(int32_t dtype, int32_t B, int32_t H, int32_t L
 #define FA_ROT_FWD(T, IL)                                                                       \
   rotary_pair_fwd_kernel<T, IL><<<pl.grid, kRotaryThreads, 0, s>>>(                             \
       static_cast<const T *>(x->ptr), strides_of(x), static_cast<T *>(out1->ptr), strides_of(out1),             \
-      static_cast<T *>(out2->ptr), strides_of(out2), t, positions, pos_stride_b, H, L, D,               \
+      static_cast<T *>(out2->ptr), strides_of(out2), t, positions, pos_stride_b, B, H, L, D,            \
       pl.heads_per_cta)
   if (dtype == FA_F16) {
     if (interleaved) FA_ROT_FWD(__half, true); else FA_ROT_FWD(__half, false);
@@ -283,7 +290,8 @@ extern "C" int fa_rotary_pair_bwd(int32_t dtype, int32_t B, int32_t H, int32_t L
 #define FA_ROT_BWD(T, IL)                                                                       \
   rotary_pair_bwd_kernel<T, IL><<<pl.grid, kRotaryThreads, 0, s>>>(                             \
       static_cast<const T *>(g1->ptr), strides_of(g1), static_cast<const T *>(g2->ptr), strides_of(g2),         \
-      static_cast<T *>(dx->ptr), strides_of(dx), t, positions, pos_stride_b, H, L, D, pl.heads_per_cta)
+      static_cast<T *>(dx->ptr), strides_of(dx), t, positions, pos_stride_b, B, H, L, D,                \
+      pl.heads_per_cta)
   if (dtype == FA_F16) {
     if (interleaved) FA_ROT_BWD(__half, true); else FA_ROT_BWD(__half, false);
   } else {

@@ -446,7 +446,9 @@ def run_rotary(args, dist, rank, world, device):
                             l2="each tensor (384 MiB) is larger than L2"),
                 roofline=dict(bound="hbm", kernel="rotary_pair_fwd_kernel", achieved=round(gbs_f, 1),
                               peak=peaks["hbm_gbs"], unit="GB/s", frac=round(gbs_f / peaks["hbm_gbs"], 4),
-                              peak_source=peaks["source"], traffic=None),
+                              peak_source=peaks["source"],
+                              traffic=1170e6 * B / 2,   # ncu capture of this shape at B=2 (profiles/)
+                              traffic_unit="bytes per launch (dram__bytes.sum, ncu)"),
                 gpu_launches=2 * steps)
 
 

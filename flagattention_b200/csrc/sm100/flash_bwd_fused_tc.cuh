@@ -65,6 +65,7 @@ struct FusedBwdParams {
   BwdTcParams base;
   float *dq_acc;   // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
   int Mpad;        // M rounded up to a multiple of 128
+  int num_n_blocks, group_size;   // launch order, see grouped_cta()
 };
 
 // fp32 add of `bytes` contiguous bytes of shared memory into global memory, done by the copy
@@ -153,7 +154,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   const AbortCtx actx{abort_flag, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const CtaCoord cta = grouped_cta(blockIdx.x, fp.num_n_blocks, p.B * p.Hk, fp.group_size);
+  const int nb = cta.blk, hk = cta.pair % p.Hk, b = cta.pair / p.Hk;
   const int G = p.H / p.Hk;
   const int n0 = nb * BN;
   const int p_seq = p.N - p.M;

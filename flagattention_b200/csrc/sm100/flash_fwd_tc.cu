@@ -35,7 +35,10 @@ static int launch_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q, co
   p.B = s->B, p.H = s->H, p.Hk = s->Hk, p.M = s->M, p.N = s->N;
   p.causal = s->causal, p.sm_scale = s->sm_scale, p.w = w;
   p.status = device_status_word();
-  dim3 grid((s->M + C::BM - 1) / C::BM, s->B * s->H, 1);
+  // the CTAs of a (batch, head) pair share its K and V (and K2 under piecewise)
+  p.num_m_blocks = (s->M + C::BM - 1) / C::BM;
+  p.group_size = cta_group_size((int64_t)s->N * D * 2 * (PW ? 3 : 2), s->B * s->H);
+  dim3 grid((unsigned)((int64_t)p.num_m_blocks * s->B * s->H), 1, 1);
   kern<<<grid, C::kThreads, C::kTotal, stream>>>(mq, mk, mv, mq2, mk2, p);
   FA_CHECK_LAUNCH();
   return FA_OK;

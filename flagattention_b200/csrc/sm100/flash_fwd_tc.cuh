@@ -29,6 +29,7 @@ struct FwdTcParams {
   float sm_scale;
   int w;  // piecewise distance threshold (PW kernels only)
   int *status;
+  int num_m_blocks, group_size;  // launch order, see grouped_cta()
 };
 
 template <int D>
@@ -75,8 +76,9 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
   const AbortCtx actx{abort_flag, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mb = gridDim.x - 1 - blockIdx.x;  // heaviest causal tiles first
-  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  const CtaCoord cta = grouped_cta(blockIdx.x, p.num_m_blocks, p.B * p.H, p.group_size);
+  const int mb = p.num_m_blocks - 1 - cta.blk;  // heaviest causal tiles first
+  const int b = cta.pair / p.H, h = cta.pair % p.H;
   const int hk = h / (p.H / p.Hk);
   const int m0 = mb * BM;
   const int p_seq = p.N - p.M;

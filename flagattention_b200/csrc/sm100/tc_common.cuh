@@ -74,6 +74,33 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ---------------------------------------------------------------------------
+// CTA launch order.  A grid is `nblk` blocks x `npairs` (batch, head) pairs, and under a causal
+// mask the cost of a block falls steadily with its index.  Numbering the CTAs pair by pair ends
+// the grid with the heavy blocks of the last few pairs running alone (a tail of several per
+// cent); numbering them heaviest-first over ALL pairs would have every resident CTA stream a
+// different pair's operands, far more than L2 holds.  So the pairs are taken in groups of `gs`
+// whose shared operands fit in L2 together, and inside a group all blocks 0 come first, then all
+// blocks 1, and so on.  The grid is one-dimensional; every group but the last has `gs` pairs.
+// ---------------------------------------------------------------------------
+struct CtaCoord {
+  int blk, pair;
+};
+__device__ __forceinline__ CtaCoord grouped_cta(unsigned id, int nblk, int npairs, int gs) {
+  const unsigned per_group = (unsigned)gs * nblk;
+  const unsigned g = id / per_group, r = id - g * per_group;
+  const int n = min(gs, npairs - (int)g * gs);
+  return CtaCoord{(int)(r / n), (int)(g * gs + r % n)};
+}
+// pairs per group: as many as keep `hot_bytes_per_pair` (the bytes the CTAs of one pair share)
+// within about a quarter of L2, at most 32
+inline int cta_group_size(int64_t hot_bytes_per_pair, int npairs) {
+  const int64_t budget = 32ll << 20;
+  int64_t gs = budget / (hot_bytes_per_pair > 0 ? hot_bytes_per_pair : 1);
+  gs = gs < 1 ? 1 : (gs > 32 ? 32 : gs);
+  return (int)(gs < npairs ? gs : (npairs > 0 ? npairs : 1));
+}
+
+// ---------------------------------------------------------------------------
 // TMA: 4-D tiled load global -> shared of this CTA only, completion on an mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap *map,

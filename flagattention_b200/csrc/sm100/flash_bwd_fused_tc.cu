@@ -63,9 +63,9 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
     return FA_ERR_LAUNCH;
   if (stages & 2) {
     // the CTAs of a (batch, kv head) pair share its Q and dO tiles and its slice of the dq workspace
-    fp.num_n_blocks = (s->N + C::BN - 1) / C::BN;
-    fp.group_size = cta_group_size((int64_t)(s->H / s->Hk) * s->M * D * 8, s->B * s->Hk);
-    dim3 grid((unsigned)((int64_t)fp.num_n_blocks * s->Hk * s->B), 1, 1);
+    p.num_blocks = (s->N + C::BN - 1) / C::BN;
+    p.group_size = cta_group_size((int64_t)(s->H / s->Hk) * s->M * D * 8, s->B * s->Hk);
+    dim3 grid((unsigned)((int64_t)p.num_blocks * s->Hk * s->B), 1, 1);
     kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, mdk, mdv, fp);
     FA_CHECK_LAUNCH();
   }

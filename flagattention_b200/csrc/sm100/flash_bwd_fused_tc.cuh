@@ -65,7 +65,6 @@ struct FusedBwdParams {
   BwdTcParams base;
   float *dq_acc;   // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
   int Mpad;        // M rounded up to a multiple of 128
-  int num_n_blocks, group_size;   // launch order, see grouped_cta()
 };
 
 // fp32 add of `bytes` contiguous bytes of shared memory into global memory, done by the copy
@@ -154,7 +153,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   const AbortCtx actx{abort_flag, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const CtaCoord cta = grouped_cta(blockIdx.x, fp.num_n_blocks, p.B * p.Hk, fp.group_size);
+  const CtaCoord cta = grouped_cta(blockIdx.x, p.num_blocks, p.B * p.Hk, p.group_size);
   const int nb = cta.blk, hk = cta.pair % p.Hk, b = cta.pair / p.Hk;
   const int G = p.H / p.Hk;
   const int n0 = nb * BN;

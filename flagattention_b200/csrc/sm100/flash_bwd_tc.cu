@@ -42,7 +42,10 @@ static int launch_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tens
   if (int st = ensure_dyn_smem(kern, C::kTotal, &done)) return st;
   BwdTcParams p = make_params(s, lse, delta, mode, w);
   p.dq = dq->ptr, p.sdq = strides_of(dq);
-  dim3 grid((s->M + C::BM - 1) / C::BM, s->B * s->H, 1);
+  // the CTAs of a (batch, head) pair share its K and V
+  p.num_blocks = (s->M + C::BM - 1) / C::BM;
+  p.group_size = cta_group_size((int64_t)s->N * D * 4, s->B * s->H);
+  dim3 grid((unsigned)((int64_t)p.num_blocks * s->B * s->H), 1, 1);
   kern<<<grid, kBwdThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
   FA_CHECK_LAUNCH();
   return FA_OK;
@@ -66,7 +69,10 @@ static int launch_dkdv(const fa_flash_shape *s, const fa_tensor4 *q, const fa_te
   BwdTcParams p = make_params(s, lse, delta, mode, w);
   p.dv_accumulate = dv_accumulate;
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
-  dim3 grid((s->N + C::BN - 1) / C::BN, s->Hk, s->B);
+  // the CTAs of a (batch, kv head) pair share its Q and dO
+  p.num_blocks = (s->N + C::BN - 1) / C::BN;
+  p.group_size = cta_group_size((int64_t)(s->H / s->Hk) * s->M * D * 4, s->B * s->Hk);
+  dim3 grid((unsigned)((int64_t)p.num_blocks * s->Hk * s->B), 1, 1);
   kern<<<grid, kDkdvThreads, C::kTotal, stream>>>(m.q, m.d_o, m.k, m.v, p);
   FA_CHECK_LAUNCH();
   return FA_OK;

@@ -38,6 +38,7 @@ struct BwdTcParams {
   int mode, w;
   int dv_accumulate;  // dK/dV kernel: add dV to what `dv` already holds (second piecewise launch)
   int *status;
+  int num_blocks, group_size;  // launch order of the two-kernel backward, see grouped_cta()
 };
 
 constexpr int kEwWarps = 16;                       // element-wise warps
@@ -103,7 +104,8 @@ __global__ void __launch_bounds__(kDkdvThreads, 1)
   const AbortCtx actx{abort_flag, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const CtaCoord cta = grouped_cta(blockIdx.x, p.num_blocks, p.B * p.Hk, p.group_size);
+  const int nb = cta.blk, hk = cta.pair % p.Hk, b = cta.pair / p.Hk;
   const int G = p.H / p.Hk;
   const int n0 = nb * BN;
   const int p_seq = p.N - p.M;
@@ -491,8 +493,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const AbortCtx actx{abort_flag, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mb = gridDim.x - 1 - blockIdx.x;  // heaviest causal tiles first
-  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  const CtaCoord cta = grouped_cta(blockIdx.x, p.num_blocks, p.B * p.H, p.group_size);
+  const int mb = p.num_blocks - 1 - cta.blk;  // heaviest causal tiles first
+  const int b = cta.pair / p.H, h = cta.pair % p.H;
   const int hk = h / (p.H / p.Hk);
   const int m0 = mb * BM;
   const int p_seq = p.N - p.M;

@@ -251,7 +251,7 @@ def run_flash(args, dist, rank, world, device):
     # results of chunk i-1 out, so both PCIe directions and the SMs stay busy; the fill and drain
     # of the pipeline are one chunk (1/16 of the step) each.
     s_in, s_cmp, s_out = (torch.cuda.Stream(device=device) for _ in range(3))
-    HG = 8 if H % 8 == 0 else H
+    HG = args.e2e_heads if H % args.e2e_heads == 0 else H   # heads per pipeline chunk
     chunks = [(bi, h0) for bi in range(B) for h0 in range(0, H, HG)]
     NS = 4   # input slots on the device
     slots = [[torch.empty((1, HG, L, D), dtype=torch.bfloat16, device=device) for _ in range(4)]
@@ -287,19 +287,25 @@ def run_flash(args, dist, rank, world, device):
         for st in (s_in, s_cmp, s_out):
             cur.wait_stream(st)
 
-    e2e_step()
+    for _ in range(3):   # untimed: allocator pools of the three streams settle
+        e2e_step()
     barrier(dist)
     t0.record()
+    marks = [t0]
     for _ in range(e2e_steps):
         e2e_step()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append(ev)
     t1.record()
     torch.cuda.synchronize()
     barrier(dist)
     e2e_ms = max_over_ranks(dist, t0.elapsed_time(t1), device) / e2e_steps
+    step_ms = [round(a.elapsed_time(b), 3) for a, b in zip(marks[:-1], marks[1:])]
     nbytes = B * H * L * D * 2
     e2e = dict(value=round(world * (fwd_f + bwd_f) / (e2e_ms * 1e-3) / 1e12, 2), unit="TFLOP/s",
                ms_per_step=round(e2e_ms, 3), h2d_bytes_per_step=4 * nbytes, d2h_bytes_per_step=4 * nbytes,
-               steps=e2e_steps)
+               steps=e2e_steps, step_ms=step_ms)
     return dict(value=value, ms_step=ms_step, roofline=roofline, e2e=e2e, clocks=clocks,
                 launches=4 * args.steps)
 
@@ -573,6 +579,7 @@ def main():
     ap.add_argument("--skip-paged", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling)")
+    ap.add_argument("--e2e-heads", type=int, default=8, help="heads per chunk of the host-buffer pipeline")
     ap.add_argument("--skip-piecewise", action="store_true")
     ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise", "rotary"],
                     help="run one workload only (profiling); the JSON line is then partial")

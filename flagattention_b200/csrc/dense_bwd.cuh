@@ -15,32 +15,45 @@ namespace fa {
 // ---------------------------------------------------------------------------
 // delta
 // ---------------------------------------------------------------------------
+// A thread owns 16 bytes of kDeltaRows rows (all loads are issued before the first use, 128 bytes
+// in flight per thread); a block stays inside one (batch, head) pair, so the only divisions are
+// one per block and shifts.
+constexpr int kDeltaRows = 4;
 template <typename T, int D>
 __global__ void bwd_delta_kernel(const void *o, Strides so, const void *d_o, Strides sdo,
-                                 float *delta, int B, int H, int M) {
+                                 float *delta, int B, int H, int M, int blocks_per_pair) {
   constexpr int LPR = D / 8;  // lanes per row
-  const int64_t rows = (int64_t)B * H * M;
-  const int64_t gidx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t row = gidx / LPR;
-  const int ch = (int)(gidx % LPR);
-  float sum = 0.f;
-  if (row < rows) {
-    const int m = (int)(row % M);
-    const int64_t bh = row / M;
-    const int b = (int)(bh / H), h = (int)(bh % H);
-    uint4 ov = *reinterpret_cast<const uint4 *>(row_ptr<T>(o, so, b, h, m) + ch * 8);
-    uint4 dv = *reinterpret_cast<const uint4 *>(row_ptr<T>(d_o, sdo, b, h, m) + ch * 8);
-    const uint32_t *ou = reinterpret_cast<const uint32_t *>(&ov);
-    const uint32_t *du = reinterpret_cast<const uint32_t *>(&dv);
+  const int bh = blockIdx.x / blocks_per_pair;
+  const int rows_per_pass = blockDim.x / LPR;
+  const int m0 = (blockIdx.x - bh * blocks_per_pair) * (rows_per_pass * kDeltaRows) +
+                 threadIdx.x / LPR;
+  const int ch = threadIdx.x % LPR;
+  const int b = bh / H, h = bh - b * H;
+  uint4 ov[kDeltaRows], dv[kDeltaRows];
+#pragma unroll
+  for (int r = 0; r < kDeltaRows; ++r) {
+    const int m = m0 + r * rows_per_pass;
+    ov[r] = dv[r] = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) {
+      ov[r] = *reinterpret_cast<const uint4 *>(row_ptr<T>(o, so, b, h, m) + ch * 8);
+      dv[r] = *reinterpret_cast<const uint4 *>(row_ptr<T>(d_o, sdo, b, h, m) + ch * 8);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kDeltaRows; ++r) {
+    const int m = m0 + r * rows_per_pass;
+    const uint32_t *ou = reinterpret_cast<const uint32_t *>(&ov[r]);
+    const uint32_t *du = reinterpret_cast<const uint32_t *>(&dv[r]);
+    float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float2 a = Elem<T>::unpack(ou[i]), c = Elem<T>::unpack(du[i]);
       sum += a.x * c.x + a.y * c.y;
     }
-  }
 #pragma unroll
-  for (int off = LPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-  if (row < rows && ch == 0) delta[row] = sum;
+    for (int off = LPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (m < M && ch == 0) delta[(int64_t)bh * M + m] = sum;
+  }
 }
 
 // 4-byte async copies of `count` floats (zero-filled past `valid`).

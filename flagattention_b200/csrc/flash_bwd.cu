@@ -12,12 +12,15 @@ struct DeltaLaunch {
   cudaStream_t stream;
   template <typename T, int D>
   int operator()() const {
-    const int64_t threads_total = (int64_t)s->B * s->H * s->M * (D / 8);
     const int threads = 256;
-    const int64_t blocks = (threads_total + threads - 1) / threads;
+    const int rows_per_block = threads / (D / 8) * kDeltaRows;
+    const int64_t blocks_per_pair = (s->M + rows_per_block - 1) / rows_per_block;
+    const int64_t blocks = blocks_per_pair * s->B * s->H;
     if (blocks > 0x7fffffff) return FA_ERR_TOO_LARGE;
+    if (blocks == 0) return FA_OK;
     bwd_delta_kernel<T, D><<<(unsigned)blocks, threads, 0, stream>>>(
-        o->ptr, strides_of(o), d_o->ptr, strides_of(d_o), delta, s->B, s->H, s->M);
+        o->ptr, strides_of(o), d_o->ptr, strides_of(d_o), delta, s->B, s->H, s->M,
+        (int)blocks_per_pair);
     FA_CHECK_LAUNCH();
     return FA_OK;
   }

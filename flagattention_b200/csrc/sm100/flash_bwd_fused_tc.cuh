@@ -721,7 +721,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 }
 
 // dq = dq_acc * scale, converted to 16 bits.  Block = 32 queries x 8 warps; warp w converts the
-// eight-column groups w, w + 8, ... of its 32 rows (lane = row: the fp32 reads are 512-byte runs).
+// sixteen-column groups w, w + 8, ... of its 32 rows (lane = row: the fp32 reads are 512-byte
+// runs, and a thread writes one whole 32-byte sector of its row).
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
     dq_convert_kernel(const float *__restrict__ acc, void *dq, Strides sdq, int H, int M, int Mpad,
@@ -735,15 +736,20 @@ __global__ void __launch_bounds__(256)
                      (m % 128) * 4;
   T *orow = row_ptr_mut<T>(dq, sdq, b, h, m);
 #pragma unroll
-  for (int g = w; g < D / 8; g += 8) {
-    const float4 lo = *reinterpret_cast<const float4 *>(src + (2 * g) * 512);
-    const float4 hi = *reinterpret_cast<const float4 *>(src + (2 * g + 1) * 512);
-    uint4 v;
-    v.x = TcElem<T>::pack(lo.x * scale, lo.y * scale);
-    v.y = TcElem<T>::pack(lo.z * scale, lo.w * scale);
-    v.z = TcElem<T>::pack(hi.x * scale, hi.y * scale);
-    v.w = TcElem<T>::pack(hi.z * scale, hi.w * scale);
-    *reinterpret_cast<uint4 *>(orow + g * 8) = v;
+  for (int g = w; g < D / 16; g += 8) {
+    float4 f[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = *reinterpret_cast<const float4 *>(src + (4 * g + i) * 512);
+    uint4 v[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      v[i].x = TcElem<T>::pack(f[2 * i].x * scale, f[2 * i].y * scale);
+      v[i].y = TcElem<T>::pack(f[2 * i].z * scale, f[2 * i].w * scale);
+      v[i].z = TcElem<T>::pack(f[2 * i + 1].x * scale, f[2 * i + 1].y * scale);
+      v[i].w = TcElem<T>::pack(f[2 * i + 1].z * scale, f[2 * i + 1].w * scale);
+    }
+    *reinterpret_cast<uint4 *>(orow + g * 16) = v[0];
+    *reinterpret_cast<uint4 *>(orow + g * 16 + 8) = v[1];
   }
 }
 

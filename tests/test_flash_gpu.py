@@ -310,3 +310,41 @@ def test_rows_without_visible_keys_are_exact_zeros_every_time(generic, monkeypat
         assert torch.count_nonzero(o[:, :, :M - N]).item() == 0
         assert torch.isinf(L[:, :, :M - N]).all() and (L[:, :, :M - N] < 0).all()
         assert torch.isfinite(o).all() and torch.isfinite(L[:, :, M - N:]).all()
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D", [(1, 33, 33, 300, 300, 64),      # 33 pairs: groups of 32 + 1
+                                           (3, 22, 11, 260, 390, 128),     # 33 kv pairs, 66 query pairs
+                                           (1, 3, 3, 12288, 12288, 128)])  # backward: groups of 2 + 1
+@pytest.mark.parametrize("causal", [True, False])
+def test_ragged_last_group_of_the_launch_order(B, Hq, Hk, M, N, D, causal):
+    """The tensor-core kernels number their CTAs over groups of (batch, head) pairs; the last group
+    may hold fewer pairs than the others.  Checked head by head (the long case would not fit the
+    oracle's score matrices otherwise), forward and both backward paths."""
+    dtype = torch.bfloat16
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 1.0, "BHTD", seed=B + Hq + M)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = fa.flash_attention(q, k, v, causal)
+    grads = torch.autograd.grad(o, (q, k, v), do)
+    os.environ["FLAGATTN_B200_BWD_TWO_KERNELS"] = "1"
+    try:
+        o2 = fa.flash_attention(q, k, v, causal)
+        grads2 = torch.autograd.grad(o2, (q, k, v), do)
+    finally:
+        os.environ.pop("FLAGATTN_B200_BWD_TWO_KERNELS", None)
+    G = Hq // Hk
+    for b in range(B):
+        for hk in range(Hk):
+            hs = slice(hk * G, (hk + 1) * G)
+            qs, ks, vs = (t.detach()[b:b + 1, s].clone().requires_grad_()
+                          for t, s in ((q, hs), (k, slice(hk, hk + 1)), (v, slice(hk, hk + 1))))
+            dos = do[b:b + 1, hs]
+            o_ref = oracle.flash_attention(qs, ks, vs, causal, upcast=True)
+            g_ref = torch.autograd.grad(o_ref, (qs, ks, vs), dos)
+            o_t = oracle.flash_attention(qs, ks, vs, causal, upcast=False)
+            g_t = torch.autograd.grad(o_t, (qs, ks, vs), dos)
+            assert_within_2x(o[b:b + 1, hs], o_ref, o_t, f"o[{b},{hk}]")
+            for name, g, g2, r, t, s in zip(("dq", "dk", "dv"), grads, grads2, g_ref, g_t,
+                                            (hs, slice(hk, hk + 1), slice(hk, hk + 1))):
+                assert_within_2x(g[b:b + 1, s], r, t, f"{name}[{b},{hk}]")
+                assert_within_2x(g2[b:b + 1, s], r, t, f"{name}[{b},{hk}] (two kernels)")
+            del o_ref, g_ref, o_t, g_t

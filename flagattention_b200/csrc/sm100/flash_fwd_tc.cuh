@@ -114,6 +114,24 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
       mbar_init(bar(PV_DONE + s), 1);
     }
     fence_barrier_init();
+    // The loads of Q and of the first K / V tile go out right here, before the TMEM allocation
+    // and the CTA-wide barrier below, so that their latency runs under the rest of the set-up.
+    if (E > 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      const bool far0 = PW && E2 > 0;
+      const int n00 = ((PW && E2 == 0) ? jf : 0) * BN;
+      mbar_expect_tx(bar(Q_FULL), C::kQBytes);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kQ + s * BM * 128, far0 ? &map_q2 : &map_q, bar(Q_FULL), s * 64, m0, h, b);
+      mbar_expect_tx(bar(K_FULL), C::kKVBytes);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kK + s * BN * 128, far0 ? &map_k2 : &map_k, bar(K_FULL), s * 64, n00, hk, b);
+      mbar_expect_tx(bar(V_FULL), C::kKVBytes);
+      for (int s = 0; s < KSUB; ++s)
+        tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(V_FULL), s * 64, n00, hk, b);
+    }
   }
   if (warp == 0) {
     tmem_alloc(smem + C::kMisc, C::kTmemCols);
@@ -127,16 +145,10 @@ __global__ void __launch_bounds__(FwdTcCfg<D>::kThreads, 2)
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && E > 0) {
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_v);
-      const CUtensorMap *first_q = (PW && E2 > 0) ? &map_q2 : &map_q;
-      mbar_expect_tx(bar(Q_FULL), C::kQBytes);
-      for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kQ + s * BM * 128, first_q, bar(Q_FULL), s * 64, m0, h, b);
-      int issued_k = 0, issued_v = 0;
+      // Q and tile 0 were requested during set-up
+      int issued_k = 1, issued_v = 1;
       bool ok = true;
-      for (int e = 0; e < E && ok; ++e) {
+      for (int e = 1; e < E && ok; ++e) {
         const bool far = PW && e < E2;
         const int j = (PW && e >= E2) ? jf + (e - E2) : e;
         const int st = e & 1, ph = (e >> 1) & 1, n0 = j * BN;

@@ -136,3 +136,44 @@ def test_single_query_dispatch_rule():
     assert not fl._decode_covered(q, kt, v)                                                 # strides differ
     tab, lens = fl._identity_block_table(2, 4, 16, "cpu")
     assert tab.tolist() == [[0, 1, 2, 3], [16, 17, 18, 19]] and lens.tolist() == [64, 64]
+
+
+def test_rotary_host_checks_and_table_normalisation():
+    """rotary_pair's host side: table dtype / shape checks, re-packing of tables the kernel cannot
+    read in place, position broadcasting; and rotary_tables against the angle formula."""
+    from flagattention_b200 import rotary
+    cos, sin = fa.rotary_tables(10, 32, base=100.0, position_scale=0.5)
+    assert cos.shape == sin.shape == (10, 16) and cos.dtype == torch.float32
+    ang = 3 * 0.5 * 100.0 ** (-2 * 5 / 32)
+    assert abs(cos[3, 5].item() - math.cos(ang)) < 1e-6 and abs(sin[3, 5].item() - math.sin(ang)) < 1e-6
+
+    good = [torch.zeros(10, 16) for _ in range(4)]
+    tabs, rows, stride = rotary._tables_ready(good, 16)
+    assert rows == 10 and stride == 16 and all(a is b for a, b in zip(tabs, good))
+    wide = [torch.zeros(10, 64) for _ in range(4)]               # more columns than D / 2: read in place
+    tabs, rows, stride = rotary._tables_ready(wide, 16)
+    assert stride == 64 and all(a is b for a, b in zip(tabs, wide))
+    odd = [torch.zeros(10, 35)[:, :16] for _ in range(4)]         # row stride 35: re-packed
+    tabs, rows, stride = rotary._tables_ready(odd, 16)
+    assert stride == 16 and all(t.is_contiguous() for t in tabs)
+    with pytest.raises(AssertionError):
+        rotary._tables_ready([torch.zeros(10, 16, dtype=torch.float64)] * 4, 16)
+    with pytest.raises(AssertionError):
+        rotary._tables_ready([torch.zeros(10, 8)] * 4, 16)        # fewer than D / 2 columns
+    with pytest.raises(AssertionError):
+        rotary._tables_ready([torch.zeros(10, 16)] * 3 + [torch.zeros(9, 16)], 16)
+
+    pos, _, stride_b = rotary._positions_ready(torch.arange(7, dtype=torch.int32), 3, 7, "cpu")
+    assert pos.dtype == torch.int64 and pos.shape == (1, 7) and stride_b == 0      # one row for the batch
+    pos, _, stride_b = rotary._positions_ready(torch.zeros(3, 7, dtype=torch.int64), 3, 7, "cpu")
+    assert stride_b == 7
+    assert rotary._positions_ready(None, 3, 7, "cpu")[0] is None
+    with pytest.raises(AssertionError):
+        rotary._positions_ready(torch.zeros(7), 3, 7, "cpu")                        # floating point
+    with pytest.raises(AssertionError):
+        rotary._positions_ready(torch.zeros(2, 7, dtype=torch.int64), 3, 7, "cpu")  # wrong batch
+
+    import inspect
+    assert list(inspect.signature(fa.rotary_pair).parameters) == [
+        "x", "cos1", "sin1", "cos2", "sin2", "positions", "interleaved"]
+    assert hasattr(fa.testing, "rotary_pair")

@@ -59,3 +59,69 @@ def max_over_ranks(value, device, group=None):
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
+
+
+def combine_partial_attention(o_a, lse_a, o_b, lse_b):
+    """Merges two attention results over disjoint key sets for the same queries, each normalised
+    over its own keys with natural-log normaliser `lse` (B, H, M): the softmax over the union is
+    o = o_a * exp(lse_a - lse) + o_b * exp(lse_b - lse), lse = logaddexp(lse_a, lse_b).  The rule of
+    the reference's split-KV combine (src/flag_attn/split_kv.py:170-227) applied to two parts; rows
+    without any key in either part (lse = -inf) stay zero.  fp32 in, fp32 out."""
+    lse = torch.logaddexp(lse_a, lse_b)
+    safe = torch.where(torch.isinf(lse) & (lse < 0), torch.zeros_like(lse), lse)
+    w_a = torch.exp(lse_a - safe).unsqueeze(-1)
+    w_b = torch.exp(lse_b - safe).unsqueeze(-1)
+    return o_a * w_a + o_b * w_b, lse
+
+
+def ring_flash_attention(q, k, v, causal=False, sm_scale=None, group=None, attention=None):
+    """Forward of flash_attention with the sequence sharded over the ranks of `group`: every rank
+    passes in ITS rows of q and ITS keys / values (equal lengths on all ranks, rank order = sequence
+    order) and gets back (o, log_normalizer) of its rows over ALL keys.
+
+    The key / value shards travel round a ring, one hop per step (point-to-point sends of the
+    process group, posted before the step's attention call so that they overlap it); each step
+    attends the local queries to the shard in hand with the ordinary single-device operator and folds
+    the result in with the log-normaliser rule of the split-KV combine.  Under `causal` the global
+    mask is bottom-right aligned over the whole sequence, which needs as many queries as keys per
+    rank: a shard from an earlier rank is fully visible, the rank's own shard is causal, later
+    shards are skipped.  Forward only (no autograd through the ring).
+
+    `attention(q, k, v, causal, sm_scale) -> (o, log_normalizer)` defaults to this package's
+    flash_attention; tests inject the PyTorch reference to run the ring on CPU ranks."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if attention is None:
+        from .flash import attention as flash_attention
+
+        def attention(q_, k_, v_, causal_, scale_):
+            o_, lse_, *_ = flash_attention(q_, k_, v_, causal=causal_, sm_scale=scale_,
+                                           return_log_normalizer=True)
+            return o_, lse_
+    if causal:
+        assert q.shape[2] == k.shape[2], "causal ring attention needs as many queries as keys per rank"
+    peer = (lambda i: dist.get_global_rank(group, i)) if group is not None else (lambda i: i)
+    nxt, prv = peer((rank + 1) % world), peer((rank - 1) % world)
+    k_cur, v_cur = k.contiguous(), v.contiguous()
+    o_acc = lse_acc = None
+    for step in range(world):
+        owner = (rank - step) % world            # whose keys / values are in hand
+        reqs = []
+        if step < world - 1:
+            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
+            ops = [dist.P2POp(dist.isend, k_cur, nxt, group), dist.P2POp(dist.isend, v_cur, nxt, group),
+                   dist.P2POp(dist.irecv, k_nxt, prv, group), dist.P2POp(dist.irecv, v_nxt, prv, group)]
+            reqs = dist.batch_isend_irecv(ops)
+        if not causal or owner <= rank:
+            o_j, lse_j = attention(q, k_cur, v_cur, causal and owner == rank, sm_scale)
+            o_j, lse_j = o_j.float(), lse_j.float()
+            if o_acc is None:
+                o_acc, lse_acc = o_j, lse_j
+            else:
+                o_acc, lse_acc = combine_partial_attention(o_acc, lse_acc, o_j, lse_j)
+        for req in reqs:
+            req.wait()
+        if step < world - 1:
+            k_cur, v_cur = k_nxt, v_nxt
+    return o_acc.to(q.dtype), lse_acc

@@ -77,3 +77,62 @@ def test_two_rank_gloo_shard_and_gather(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def _ring_worker(rank, world, port, result_dir):
+    import torch.distributed as dist
+    from flagattention_b200 import testing
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        def attention(q, k, v, causal, sm_scale):
+            o, lse, _ = testing.flash_attention(q, k, v, causal, sm_scale=sm_scale,
+                                                return_log_normalizer=True, upcast=True)
+            return o, lse
+
+        gen = torch.Generator().manual_seed(7)                 # same full tensors on every rank
+        B, Hq, Hk, D, m = 2, 4, 2, 32, 24                     # m rows / keys per rank
+        L = m * world
+        q = torch.randn((B, Hq, L, D), generator=gen)
+        k = torch.randn((B, Hk, L, D), generator=gen)
+        v = torch.randn((B, Hk, L, D), generator=gen)
+        rows = slice(rank * m, (rank + 1) * m)
+        for causal in (False, True):
+            o, lse = fdist.ring_flash_attention(q[:, :, rows], k[:, :, rows], v[:, :, rows], causal, None,
+                                                attention=attention)
+            o_full, lse_full, _ = testing.flash_attention(q, k, v, causal, return_log_normalizer=True,
+                                                          upcast=True)
+            assert torch.allclose(o, o_full[:, :, rows], atol=1e-5, rtol=1e-5), causal
+            assert torch.allclose(lse, lse_full[:, :, rows], atol=1e-5, rtol=1e-5), causal
+        # non-causal with more keys than queries per rank (a decode-like shard)
+        kk = torch.randn((B, Hk, 40 * world, D), generator=gen)
+        vv = torch.randn((B, Hk, 40 * world, D), generator=gen)
+        keys = slice(rank * 40, (rank + 1) * 40)
+        o, lse = fdist.ring_flash_attention(q[:, :, rows], kk[:, :, keys], vv[:, :, keys], False, 0.2,
+                                            attention=attention)
+        o_full, lse_full, _ = testing.flash_attention(q[:, :, rows], kk, vv, False, sm_scale=0.2,
+                                                      return_log_normalizer=True, upcast=True)
+        assert torch.allclose(o, o_full, atol=1e-5, rtol=1e-5)
+        assert torch.allclose(lse, lse_full, atol=1e-5, rtol=1e-5)
+        open(os.path.join(result_dir, f"ring{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_ring_attention_over_gloo_ranks(tmp_path, world):
+    """Context-parallel forward: the ring exchange and the log-normaliser combine on CPU ranks, with
+    the PyTorch reference standing in for the single-device operator."""
+    mp.spawn(_ring_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ring{r}").exists() for r in range(world))
+
+
+def test_combine_partial_attention_handles_rows_without_keys():
+    o_a, o_b = torch.ones(1, 1, 3, 2), 3 * torch.ones(1, 1, 3, 2)
+    lse_a = torch.tensor([[[0.0, float("-inf"), float("-inf")]]])
+    lse_b = torch.tensor([[[0.0, 1.0, float("-inf")]]])
+    o, lse = fdist.combine_partial_attention(o_a, lse_a, o_b * torch.tensor([1.0, 1.0, 0.0])[None, None, :, None],
+                                             lse_b)
+    assert torch.allclose(o[0, 0, 0], torch.tensor([2.0, 2.0]))          # equal weights
+    assert torch.allclose(o[0, 0, 1], torch.tensor([3.0, 3.0]))          # only part b has keys
+    assert torch.equal(o[0, 0, 2], torch.zeros(2)) and lse[0, 0, 2] == float("-inf")

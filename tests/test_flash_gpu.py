@@ -348,3 +348,19 @@ def test_ragged_last_group_of_the_launch_order(B, Hq, Hk, M, N, D, causal):
                 assert_within_2x(g[b:b + 1, s], r, t, f"{name}[{b},{hk}]")
                 assert_within_2x(g2[b:b + 1, s], r, t, f"{name}[{b},{hk}] (two kernels)")
             del o_ref, g_ref, o_t, g_t
+
+
+def test_ring_attention_of_one_rank_is_flash_attention(tmp_path):
+    """The context-parallel forward with its default operator (this package's flash_attention), on a
+    process group of one rank: no exchange, the same result as the direct call."""
+    import torch.distributed as dist
+    from flagattention_b200 import dist as fdist
+    dist.init_process_group("gloo", init_method=f"file://{tmp_path}/pg", rank=0, world_size=1)
+    try:
+        q, k, v, _ = make_qkv(2, 4, 2, 300, 300, 64, torch.float16, "cuda", seed=77)
+        for causal in (True, False):
+            o, lse = fdist.ring_flash_attention(q, k, v, causal)
+            o_ref, lse_ref, *_ = fa.flash_attention(q, k, v, causal=causal, return_log_normalizer=True)
+            assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+    finally:
+        dist.destroy_process_group()

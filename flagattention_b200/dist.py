@@ -4,6 +4,9 @@ The operators are stateless and per-device, and every (batch, head) pair of flas
 attention and every sequence of paged attention is independent, so a multi-GPU run needs no
 collective on the data path: each rank computes its shard, and one all_gather reassembles the
 outputs only where a consumer wants the full tensor.
+
+The exception is a sequence too long for one GPU: ring_flash_attention shards the SEQUENCE over
+the ranks and passes key / value shards round a ring (forward only).
 """
 import torch
 

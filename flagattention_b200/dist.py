@@ -77,45 +77,16 @@ def combine_partial_attention(o_a, lse_a, o_b, lse_b):
     return o_a * w_a + o_b * w_b, lse
 
 
-def ring_flash_attention(q, k, v, causal=False, sm_scale=None, group=None, attention=None):
-    """Forward of flash_attention with the sequence sharded over the ranks of `group`: every rank
-    passes in ITS rows of q and ITS keys / values (equal lengths on all ranks, rank order = sequence
-    order) and gets back (o, log_normalizer) of its rows over ALL keys.
-
-    The key / value shards travel round a ring, one hop per step (point-to-point sends of the
-    process group, posted before the step's attention call so that they overlap it); each step
-    attends the local queries to the shard in hand with the ordinary single-device operator and folds
-    the result in with the log-normaliser rule of the split-KV combine.  Under `causal` the global
-    mask is bottom-right aligned over the whole sequence, which needs as many queries as keys per
-    rank: a shard from an earlier rank is fully visible, the rank's own shard is causal, later
-    shards are skipped.  Forward only (no autograd through the ring).
-
-    `attention(q, k, v, causal, sm_scale) -> (o, log_normalizer)` defaults to this package's
-    flash_attention; tests inject the PyTorch reference to run the ring on CPU ranks."""
-    import torch.distributed as dist
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    if attention is None:
-        from .flash import attention as flash_attention
-
-        def attention(q_, k_, v_, causal_, scale_):
-            o_, lse_, *_ = flash_attention(q_, k_, v_, causal=causal_, sm_scale=scale_,
-                                           return_log_normalizer=True)
-            return o_, lse_
+def _ring_forward(q, k, v, causal, sm_scale, group, attention):
+    """The forward ring: returns (o, log_normalizer) of the local queries over all ranks' keys."""
+    world, rank, nxt, prv = _ring_peers(group)
     if causal:
         assert q.shape[2] == k.shape[2], "causal ring attention needs as many queries as keys per rank"
-    peer = (lambda i: dist.get_global_rank(group, i)) if group is not None else (lambda i: i)
-    nxt, prv = peer((rank + 1) % world), peer((rank - 1) % world)
     k_cur, v_cur = k.contiguous(), v.contiguous()
     o_acc = lse_acc = None
     for step in range(world):
         owner = (rank - step) % world            # whose keys / values are in hand
-        reqs = []
-        if step < world - 1:
-            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
-            ops = [dist.P2POp(dist.isend, k_cur, nxt, group), dist.P2POp(dist.isend, v_cur, nxt, group),
-                   dist.P2POp(dist.irecv, k_nxt, prv, group), dist.P2POp(dist.irecv, v_nxt, prv, group)]
-            reqs = dist.batch_isend_irecv(ops)
+        reqs, kv_nxt = ([], None) if step == world - 1 else _exchange([k_cur, v_cur], nxt, prv, group)
         if not causal or owner <= rank:
             o_j, lse_j = attention(q, k_cur, v_cur, causal and owner == rank, sm_scale)
             o_j, lse_j = o_j.float(), lse_j.float()
@@ -125,6 +96,105 @@ def ring_flash_attention(q, k, v, causal=False, sm_scale=None, group=None, atten
                 o_acc, lse_acc = combine_partial_attention(o_acc, lse_acc, o_j, lse_j)
         for req in reqs:
             req.wait()
-        if step < world - 1:
-            k_cur, v_cur = k_nxt, v_nxt
+        if kv_nxt is not None:
+            k_cur, v_cur = kv_nxt
     return o_acc.to(q.dtype), lse_acc
+
+
+def _ring_peers(group):
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    peer = (lambda i: dist.get_global_rank(group, i)) if group is not None else (lambda i: i)
+    return world, rank, peer((rank + 1) % world), peer((rank - 1) % world)
+
+
+def _exchange(tensors, nxt, prv, group):
+    """Posts the sends of `tensors` to the next rank and the receives of their successors from the
+    previous one; returns (requests, received tensors)."""
+    import torch.distributed as dist
+    recv = [torch.empty_like(t) for t in tensors]
+    ops = [dist.P2POp(dist.isend, t, nxt, group) for t in tensors] + \
+          [dist.P2POp(dist.irecv, t, prv, group) for t in recv]
+    return dist.batch_isend_irecv(ops), recv
+
+
+def _ring_backward(q, k, v, o, lse, do, causal, sm_scale, group, backward):
+    """Gradients of the ring forward.  `backward(q, k, v, o, lse, do, causal, sm_scale)` is the
+    single-device backward evaluated with the GLOBAL o and log-normaliser of the local rows, so what
+    it returns for the shard in hand are that shard's exact contributions: dq is summed locally, and
+    the dk / dv of a shard travel round the ring WITH the shard (fp32), arriving back at its owner
+    after the last hop."""
+    world, rank, nxt, prv = _ring_peers(group)
+    k_cur, v_cur = k.contiguous(), v.contiguous()
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    dk_cur = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
+    dv_cur = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
+    for step in range(world):
+        owner = (rank - step) % world
+        kv_reqs, kv_nxt = ([], None) if step == world - 1 else _exchange([k_cur, v_cur], nxt, prv, group)
+        if not causal or owner <= rank:
+            dq_j, dk_j, dv_j = backward(q, k_cur, v_cur, o, lse, do, causal and owner == rank, sm_scale)
+            dq += dq_j.float()
+            dk_cur += dk_j.float()
+            dv_cur += dv_j.float()
+        g_reqs = []
+        if world > 1:
+            g_reqs, (dk_cur, dv_cur) = _exchange([dk_cur, dv_cur], nxt, prv, group)
+        for req in kv_reqs + g_reqs:
+            req.wait()
+        if kv_nxt is not None:
+            k_cur, v_cur = kv_nxt
+    return dq.to(q.dtype), dk_cur.to(k.dtype), dv_cur.to(v.dtype)
+
+
+class _RingFlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, group, attention, backward):
+        o, lse = _ring_forward(q, k, v, causal, sm_scale, group, attention)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.args = (causal, sm_scale, group, backward)
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, sm_scale, group, backward = ctx.args
+        dq, dk, dv = _ring_backward(q, k, v, o, lse, do.contiguous(), causal, sm_scale, group, backward)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def ring_flash_attention(q, k, v, causal=False, sm_scale=None, group=None, attention=None, backward=None):
+    """flash_attention with the SEQUENCE sharded over the ranks of `group`: every rank passes in ITS
+    rows of q and ITS keys / values (equal lengths on all ranks, rank order = sequence order) and gets
+    back (o, log_normalizer) of its rows over ALL keys; differentiable with respect to q, k, v.
+
+    The key / value shards travel round a ring, one hop per step (point-to-point sends of the
+    process group, posted before the step's attention call so that they overlap it); each step
+    attends the local queries to the shard in hand with the ordinary single-device operator and folds
+    the result in with the log-normaliser rule of the split-KV combine.  Under `causal` the global
+    mask is bottom-right aligned over the whole sequence, which needs as many queries as keys per
+    rank: a shard from an earlier rank is fully visible, the rank's own shard is causal, later
+    shards are skipped.  The backward makes the same tour with the single-device backward kernels,
+    fed the global o and log-normaliser; every rank of the group must call it.
+
+    `attention(q, k, v, causal, sm_scale) -> (o, log_normalizer)` and
+    `backward(q, k, v, o, log_normalizer, do, causal, sm_scale) -> (dq, dk, dv)` default to this
+    package's kernels; tests inject PyTorch statements of both to run the ring on CPU ranks."""
+    if sm_scale is None:
+        sm_scale = q.shape[-1] ** -0.5
+    if attention is None:
+        from .flash import attention as flash_attention
+
+        def attention(q_, k_, v_, causal_, scale_):
+            o_, lse_, *_ = flash_attention(q_, k_, v_, causal=causal_, sm_scale=scale_,
+                                           return_log_normalizer=True)
+            return o_, lse_
+    if backward is None:
+        from . import _C
+        from .flash import _backward
+
+        def backward(q_, k_, v_, o_, lse_, do_, causal_, scale_):
+            q_, k_, v_, o_ = (_C.kernel_ready(t) for t in (q_, k_, v_, o_))
+            return _backward(q_, k_, v_, o_, lse_.contiguous(), do_, causal_, scale_)
+    return _RingFlashAttention.apply(q, k, v, causal, sm_scale, group, attention, backward)

@@ -90,6 +90,22 @@ def _ring_worker(rank, world, port, result_dir):
                                                 return_log_normalizer=True, upcast=True)
             return o, lse
 
+        def backward(q, k, v, o, lse, do, causal, sm_scale):
+            """The flash backward in plain fp32 torch, given the log-normaliser: P = exp(S - lse),
+            dS = P * (dP - rowsum(o * do)); group sums for dk, dv."""
+            G = q.shape[1] // k.shape[1]
+            kx, vx = k.repeat_interleave(G, dim=1), v.repeat_interleave(G, dim=1)
+            S = q @ kx.transpose(-1, -2) * sm_scale
+            if causal:
+                M, N = S.shape[-2:]
+                keep = (torch.arange(M)[:, None] + (N - M)) >= torch.arange(N)
+                S = S.masked_fill(~keep, float("-inf"))
+            P = torch.exp(S - lse[..., None])
+            dS = P * (do @ vx.transpose(-1, -2) - (o * do).sum(-1, keepdim=True)) * sm_scale
+            dq, dk, dv = dS @ kx, dS.transpose(-1, -2) @ q, P.transpose(-1, -2) @ do
+            fold = lambda t: t.reshape(t.shape[0], k.shape[1], G, *t.shape[2:]).sum(2)
+            return dq, fold(dk), fold(dv)
+
         gen = torch.Generator().manual_seed(7)                 # same full tensors on every rank
         B, Hq, Hk, D, m = 2, 4, 2, 32, 24                     # m rows / keys per rank
         L = m * world
@@ -104,6 +120,17 @@ def _ring_worker(rank, world, port, result_dir):
                                                           upcast=True)
             assert torch.allclose(o, o_full[:, :, rows], atol=1e-5, rtol=1e-5), causal
             assert torch.allclose(lse, lse_full[:, :, rows], atol=1e-5, rtol=1e-5), causal
+            # gradients: the ring's tour against autograd through the reference on the full sequence
+            do = torch.randn((B, Hq, L, D), generator=torch.Generator().manual_seed(11))
+            qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+            o_ref = testing.flash_attention(qf, kf, vf, causal, upcast=True)
+            g_full = torch.autograd.grad(o_ref, (qf, kf, vf), do)
+            ql, kl, vl = (t[:, :, rows].clone().requires_grad_() for t in (q, k, v))
+            o_l, _ = fdist.ring_flash_attention(ql, kl, vl, causal, None, attention=attention,
+                                                backward=backward)
+            g = torch.autograd.grad(o_l, (ql, kl, vl), do[:, :, rows])
+            for name, a, b in zip(("dq", "dk", "dv"), g, g_full):
+                assert torch.allclose(a, b[:, :, rows], atol=2e-5, rtol=1e-4), (name, causal)
         # non-causal with more keys than queries per rank (a decode-like shard)
         kk = torch.randn((B, Hk, 40 * world, D), generator=gen)
         vv = torch.randn((B, Hk, 40 * world, D), generator=gen)

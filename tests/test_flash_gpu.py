@@ -362,5 +362,13 @@ def test_ring_attention_of_one_rank_is_flash_attention(tmp_path):
             o, lse = fdist.ring_flash_attention(q, k, v, causal)
             o_ref, lse_ref, *_ = fa.flash_attention(q, k, v, causal=causal, return_log_normalizer=True)
             assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+        # and its backward is the operator's backward (dq of the one-pass kernel: fp32 rounding only)
+        q, k, v, do = make_qkv(1, 4, 2, 260, 260, 128, torch.bfloat16, "cuda", seed=78)
+        q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+        o, _ = fdist.ring_flash_attention(q, k, v, True)
+        g = torch.autograd.grad(o, (q, k, v), do)
+        g_ref = torch.autograd.grad(fa.flash_attention(q, k, v, causal=True), (q, k, v), do)
+        assert torch.equal(g[1], g_ref[1]) and torch.equal(g[2], g_ref[2])
+        assert max_diff(g[0], g_ref[0]) <= 2 ** -7 * g_ref[0].float().abs().max().item()
     finally:
         dist.destroy_process_group()

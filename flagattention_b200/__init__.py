@@ -13,4 +13,5 @@ from .split_kv import attention as flash_attention_split_kv  # noqa: F401
 from .paged import attention as paged_attention  # noqa: F401
 from .paged import reshape_and_cache  # noqa: F401  (writer of the paged caches; no reference counterpart)
 from .rotary import rotary_pair, rotary_tables  # noqa: F401  (producer of piecewise_attention's operands)
+from . import dist  # noqa: F401  (shard helpers, ring attention over a process group)
 from . import testing  # noqa: F401

@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = (
     "fa_paged_attention_noalloc", "fa_dropout_mask",
     "fa_flash_bwd_fused", "fa_flash_bwd_fused_stages", "fa_flash_bwd_fused_workspace_bytes", "fa_piecewise_bwd_fused",
     "fa_paged_cache_append", "fa_rotary_pair_fwd", "fa_rotary_pair_bwd",
-    "fa_device_status", "fa_status_string", "fa_version",
+    "fa_device_status", "fa_debug_wait_probe", "fa_set_kernel_family", "fa_status_string", "fa_version",
 )
 
 
@@ -83,8 +83,32 @@ def load():
             lib.fa_flash_bwd_fused_workspace_bytes.restype = ctypes.c_int64
             lib.fa_num_splits_heuristic.restype = ctypes.c_int32
             lib.fa_num_splits_heuristic.argtypes = [ctypes.c_int32] * 8
+            lib.fa_debug_wait_probe.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+            lib.fa_set_kernel_family.argtypes = [ctypes.c_int32]
+            lib.fa_set_kernel_family.restype = ctypes.c_int32
             _lib = lib
     return _lib
+
+
+FA_ERR_UNSUPPORTED = -2
+
+
+class kernel_family:
+    """Context manager around fa_set_kernel_family: `with kernel_family("generic"):` runs the
+    flash / piecewise operators on the shape-generic kernels only, "auto" on the tcgen05 kernels
+    wherever they cover the call.  Process-wide while active."""
+
+    def __init__(self, family):
+        assert family in ("auto", "generic")
+        self.family = 1 if family == "generic" else 0
+
+    def __enter__(self):
+        self.previous = load().fa_set_kernel_family(self.family)
+        return self
+
+    def __exit__(self, *exc):
+        load().fa_set_kernel_family(self.previous)
+        return False
 
 
 def check(status, what):

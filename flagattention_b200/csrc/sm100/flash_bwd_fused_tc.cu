@@ -13,14 +13,8 @@ namespace tc {
 
 bool generic_forced();
 
-// FLAGATTN_B200_BWD_TWO_KERNELS=1 turns the one-pass kernel off (the tests cross-check both).
-static bool fused_disabled() {
-  const char *e = std::getenv("FLAGATTN_B200_BWD_TWO_KERNELS");
-  return e && e[0] == '1';
-}
-
 static bool fused_covered(const fa_flash_shape *s) {
-  return !generic_forced() && !fused_disabled() && s->sm_scale > 0.f &&
+  return !generic_forced() && s->sm_scale > 0.f &&
          (s->D == 64 || s->D == 128) && s->dropout_p == 0.f;
 }
 

@@ -1,4 +1,5 @@
 // Launcher of the tcgen05 flash_attention forward.
+#include <atomic>
 #include <cstdlib>
 
 #include "flash_fwd_tc.cuh"
@@ -10,10 +11,15 @@ int *device_status_word();
 
 namespace tc {
 
-bool generic_forced() {
+// Kernel family switch (fa_set_kernel_family): 0 = tcgen05 kernels wherever they cover the call,
+// 1 = shape-generic kernels only.  The environment variable FLAGATTN_B200_GENERIC=1 only sets the
+// value the process starts with.
+static std::atomic<int> g_kernel_family{[] {
   const char *e = std::getenv("FLAGATTN_B200_GENERIC");
-  return e && e[0] == '1';
-}
+  return (e && e[0] == '1') ? 1 : 0;
+}()};
+bool generic_forced() { return g_kernel_family.load(std::memory_order_relaxed) == 1; }
+int set_kernel_family(int family) { return g_kernel_family.exchange(family == 1 ? 1 : 0); }
 
 template <typename T, int D, bool PW>
 static int launch_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q, const fa_tensor4 *k,
@@ -74,3 +80,5 @@ int piecewise_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q1, const
 
 }  // namespace tc
 }  // namespace fa
+
+extern "C" int32_t fa_set_kernel_family(int32_t family) { return fa::tc::set_kernel_family(family); }

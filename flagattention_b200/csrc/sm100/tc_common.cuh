@@ -48,9 +48,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Returns false when the wait was abandoned (timeout here or abort raised elsewhere).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx &ctx,
-                                          int where) {
+// Returns false when the wait was abandoned (out of time here, or abort raised elsewhere).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, const AbortCtx &ctx,
+                                                int where, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -58,12 +58,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*ctx.smem_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *ctx.smem_flag = 1;
       if (ctx.status) atomicCAS(ctx.status, 0, where);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx &ctx,
+                                          int where) {
+  return mbar_wait_limit(bar, parity, ctx, where, kWaitCycles);
 }
 
 __device__ __forceinline__ void fence_barrier_init() {

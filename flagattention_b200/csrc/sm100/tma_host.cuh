@@ -31,12 +31,18 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // Tensor map over a (B, H, L, D) 16-bit tensor; a box is `box_rows` rows of 64
 // elements (128 bytes, 128-byte swizzle) of one (b, h).  Coordinates are
-// (d, l, h, b).  Rows past L read as zeros.  Returns false when the driver
-// rejects the layout (the caller then uses the shape-generic kernels).
+// (d, l, h, b).  Rows past L read as zeros.  A stride of 0 is accepted only on
+// a dimension of extent 1 (where it is never multiplied by anything but 0 and
+// a placeholder takes its place in the map); on a longer dimension it means a
+// broadcast view (`expand`), which a tensor map cannot express.  Returns false
+// for that, and when the driver rejects the layout: the caller then uses the
+// shape-generic kernels, which index with the true strides.
 inline bool make_map_bhld(CUtensorMap *map, const fa_tensor4 *t, int dtype, int B, int H, int L,
                           int D, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
+  if ((t->stride_l == 0 && L > 1) || (t->stride_h == 0 && H > 1) || (t->stride_b == 0 && B > 1))
+    return false;
   const int64_t sl = t->stride_l ? t->stride_l : D;
   const int64_t sh = t->stride_h ? t->stride_h : (int64_t)L * sl;
   const int64_t sb = t->stride_b ? t->stride_b : (int64_t)H * sh;

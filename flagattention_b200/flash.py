@@ -16,7 +16,53 @@ from .dropout import philox_cuda_seed_offset
 from .split_kv import get_fwd_config as get_fwd_config_kv_split
 from .split_kv import num_splits_herustic, _splitkv_forward
 
-__all__ = ["attention"]
+__all__ = ["attention", "set_backward_mode", "get_backward_mode", "backward_mode"]
+
+# Which kernels compute the gradients at head_dim 64 / 128:
+#   "one_pass"   one kernel for dq, dk, dv (five matrix products per tile); dq is summed with fp32
+#                reductions in global memory, so it is reproducible to fp32 rounding only;
+#   "two_kernel" a dK/dV kernel and a dQ kernel without any global reduction or atomic (seven
+#                products per tile), the split of the reference (src/flag_attn/flash.py:204-249):
+#                every gradient is bitwise reproducible;
+#   "auto"       (default) "two_kernel" while torch.are_deterministic_algorithms_enabled(),
+#                else "one_pass".
+_BACKWARD_MODES = ("auto", "one_pass", "two_kernel")
+_backward_mode = "auto"
+
+
+def set_backward_mode(mode):
+    """Selects the backward kernels of flash_attention and piecewise_attention (see above);
+    returns the previous mode."""
+    global _backward_mode
+    assert mode in _BACKWARD_MODES, f"mode must be one of {_BACKWARD_MODES}"
+    previous, _backward_mode = _backward_mode, mode
+    return previous
+
+
+def get_backward_mode():
+    return _backward_mode
+
+
+class backward_mode:
+    """`with backward_mode("two_kernel"): loss.backward()`"""
+
+    def __init__(self, mode):
+        assert mode in _BACKWARD_MODES, f"mode must be one of {_BACKWARD_MODES}"
+        self.mode = mode
+
+    def __enter__(self):
+        self.previous = set_backward_mode(self.mode)
+        return self
+
+    def __exit__(self, *exc):
+        set_backward_mode(self.previous)
+        return False
+
+
+def use_one_pass_backward():
+    if _backward_mode == "auto":
+        return not torch.are_deterministic_algorithms_enabled()
+    return _backward_mode == "one_pass"
 
 
 def get_fwd_config(B, H, M, N, D, causal):
@@ -165,7 +211,8 @@ def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None, dropout_p=0.0, see
         _C.check(st, "fa_flash_bwd_delta")
         if mark:
             mark("delta")
-        ws_bytes = lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+        ws_bytes = (lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+                    if use_one_pass_backward() else 0)
         if ws_bytes > 0:
             # one pass over the score tiles; dq is accumulated in an fp32 workspace
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
@@ -174,12 +221,18 @@ def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None, dropout_p=0.0, see
                     _C.fptr(ws), ctypes.c_int64(ws_bytes))
             if mark:
                 # the three parts of the call one by one, so that each can be timed
+                st = 0
                 for stage, name in ((1, "dq_zero"), (2, "dkdvdq"), (4, "dq_convert")):
-                    _C.check(lib.fa_flash_bwd_fused_stages(*args, stage, stream), "fa_flash_bwd_fused_stages")
+                    st = lib.fa_flash_bwd_fused_stages(*args, stage, stream)
+                    if st != 0:
+                        break
                     mark(name)
             else:
-                _C.check(lib.fa_flash_bwd_fused(*args, stream), "fa_flash_bwd_fused")
-            return dq, dk, dv
+                st = lib.fa_flash_bwd_fused(*args, stream)
+            # a layout the one-pass kernel cannot map (a broadcast stride) goes to the pair below
+            if st != _C.FA_ERR_UNSUPPORTED:
+                _C.check(st, "fa_flash_bwd_fused")
+                return dq, dk, dv
         st = lib.fa_flash_bwd_dkdv(_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv),
                                    _C.byref(tdo), _C.fptr(L), _C.fptr(delta), _C.byref(tdk),
                                    _C.byref(tdv), stream)

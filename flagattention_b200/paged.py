@@ -57,6 +57,9 @@ def attention(query, key_cache, value_cache, context_lens, block_tables, attn_sc
     assert key_cache.stride() == value_cache.stride(), "key and value cache must share strides"
     assert query.is_cuda and query.dtype == key_cache.dtype == value_cache.dtype
     assert block_tables.dtype in (torch.int32, torch.int64)
+    for name, t in (("key_cache", key_cache), ("value_cache", value_cache),
+                    ("context_lens", context_lens), ("block_tables", block_tables)):
+        assert t.device == query.device, f"{name} is on {t.device}, query on {query.device}"
 
     if context_lens.dtype != torch.int32:
         context_lens = context_lens.to(torch.int32)
@@ -126,6 +129,10 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
     assert key_cache.stride(-1) == 1 and all(s % 8 == 0 for s in key_cache.stride()[:-1]), \
         "caches need unit inner stride and 16-byte aligned rows"
     assert slot_mapping.numel() == num_tokens
+    assert key.is_cuda, "inputs must be CUDA tensors"
+    for name, t in (("value", value), ("key_cache", key_cache), ("value_cache", value_cache),
+                    ("slot_mapping", slot_mapping)):
+        assert t.device == key.device, f"{name} is on {t.device}, key on {key.device}"
     if key.stride() != value.stride() or key.stride(-1) != 1 or any(s % 8 for s in key.stride()[:-1]) \
             or key.data_ptr() % 16 or value.data_ptr() % 16:
         key, value = key.contiguous(), value.contiguous()

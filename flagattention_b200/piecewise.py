@@ -10,6 +10,7 @@ import math
 import torch
 
 from . import _C
+from .flash import use_one_pass_backward
 
 __all__ = ["attention"]
 
@@ -22,6 +23,9 @@ class PiecewiseAttention(torch.autograd.Function):
         assert Dk1 in {16, 32, 64, 128}
         assert q1.shape == q2.shape and k1.shape == k2.shape == v.shape
         assert q1.shape[1] == k1.shape[1], "piecewise attention has no grouped-query mode"
+        assert q1.is_cuda, "inputs must be CUDA tensors"
+        assert all(x.device == q1.device for x in (k1, q2, k2, v)), "inputs must share a device"
+        assert q1.dtype == k1.dtype == q2.dtype == k2.dtype == v.dtype
 
         B, H, M, D = q1.shape
         N = k1.shape[2]
@@ -67,7 +71,8 @@ class PiecewiseAttention(torch.autograd.Function):
             dk1 = torch.empty(k1.shape, dtype=k1.dtype, device=k1.device)
             dk2 = torch.empty(k2.shape, dtype=k2.dtype, device=k2.device)
             dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-            ws_bytes = lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+            ws_bytes = (lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+                        if use_one_pass_backward() else 0)
             if ws_bytes > 0:
                 # one pass per branch over the score tiles; dq1 / dq2 accumulate in an fp32 workspace
                 dq1 = torch.empty(q1.shape, dtype=q1.dtype, device=q1.device)
@@ -78,8 +83,10 @@ class PiecewiseAttention(torch.autograd.Function):
                                                 _C.byref(tdo), _C.fptr(L), _C.fptr(delta),
                                                 *[_C.byref(t) for t in outs], _C.fptr(ws),
                                                 ctypes.c_int64(ws_bytes), stream)
-                _C.check(st, "fa_piecewise_bwd_fused")
-                return dq1, dk1, dq2, dk2, dv, None, None, None
+                # a layout the one-pass kernel cannot map (a broadcast stride) goes to the pair below
+                if st != _C.FA_ERR_UNSUPPORTED:
+                    _C.check(st, "fa_piecewise_bwd_fused")
+                    return dq1, dk1, dq2, dk2, dv, None, None, None
             outs = [_C.tensor4(x) for x in (dk1, dk2, dv)]
             st = lib.fa_piecewise_bwd_dkdv(_C.byref(shape), w, *[_C.byref(t) for t in ins],
                                            _C.byref(tdo), _C.fptr(L), _C.fptr(delta),

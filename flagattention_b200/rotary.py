@@ -26,7 +26,10 @@ def rotary_tables(num_positions, head_dim, base=10000.0, position_scale=1.0, dev
     return ang.cos().to(device), ang.sin().to(device)
 
 
-def _tables_ready(tables, half):
+def _tables_ready(tables, half, device):
+    for t in tables:
+        assert t.device == device, \
+            f"cos / sin tables are on {t.device}, x on {device} (rotary_tables(..., device=x.device))"
     rows, stride = tables[0].shape[0], tables[0].stride(0)
     ok = True
     for t in tables:
@@ -57,8 +60,9 @@ class RotaryPair(torch.autograd.Function):
         assert x.dim() == 4, "x is (batch, heads, length, head_dim)"
         B, H, L, D = x.shape
         assert D % 16 == 0 and D <= 512, "head_dim must be a multiple of 16, at most 512"
+        assert x.is_cuda, "x must be a CUDA tensor"
         x = _C.kernel_ready(x)
-        tables, rows, stride = _tables_ready([cos1, sin1, cos2, sin2], D // 2)
+        tables, rows, stride = _tables_ready([cos1, sin1, cos2, sin2], D // 2, x.device)
         pos, pos_ptr, pos_stride = _positions_ready(positions, B, L, x.device)
         out1, out2 = torch.empty_like(x), torch.empty_like(x)
         lib = _C.load()
@@ -79,6 +83,7 @@ class RotaryPair(torch.autograd.Function):
         saved = ctx.saved_tensors
         tables = saved[:4]
         pos_ptr = _C.fptr(saved[4]) if has_pos else ctypes.c_void_p(0)
+        assert g1.device == g2.device == tables[0].device, "gradients must be on the tables' device"
         g1, g2 = _C.kernel_ready(g1), _C.kernel_ready(g2)
         B, H, L, D = g1.shape
         dx = torch.empty_like(g1)

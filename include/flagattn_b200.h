@@ -40,7 +40,12 @@ typedef enum fa_status {
 
 typedef enum fa_dtype { FA_F16 = 0, FA_BF16 = 1 } fa_dtype;
 
-/* A (B, H, L, D) operand with arbitrary b/h/l element strides, d-stride 1. */
+/* A (B, H, L, D) operand with arbitrary b/h/l element strides, d-stride 1.
+ * Stride 0: ignored on a dimension of extent 1; on a longer dimension it is a
+ * broadcast view (every index reads the same rows, e.g. one K/V head expanded
+ * over the query heads, or a prefix shared by the batch) and is honoured for
+ * INPUTS: such calls run on the shape-generic kernels, since a TMA tensor map
+ * cannot express it.  Outputs must not overlap themselves. */
 typedef struct fa_tensor4 {
   void *ptr;
   int64_t stride_b, stride_h, stride_l;
@@ -126,7 +131,12 @@ int fa_flash_bwd_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tenso
  * tensor-core path): S and dP are computed once instead of once per kernel.  Replaces the pair
  * of launches `_bwd_kv_kernel` + `_bwd_q_kernel` (src/flag_attn/flash.py:204-249).  dq is
  * accumulated with fp32 global reductions in `workspace`, so it is reproducible to fp32
- * rounding only (dk, dv are bitwise reproducible).
+ * rounding only (dk, dv are bitwise reproducible).  A caller that needs bitwise reproducible
+ * gradients (the `_bwd_q_kernel` contract: "no atomics") calls fa_flash_bwd_dkdv + fa_flash_bwd_dq
+ * instead: which of the two a process uses is the caller's choice of entry point, nothing else
+ * (the Python host chooses by torch.are_deterministic_algorithms_enabled() or
+ * flagattention_b200.flash.set_backward_mode()).  A layout that a tensor map cannot express
+ * (a broadcast stride) also returns FA_ERR_UNSUPPORTED here; the pair of calls then serves it.
  * fa_flash_bwd_fused_workspace_bytes returns the bytes of device memory `workspace` must hold
  * (16-byte aligned), or 0 when the shape is not covered: then call fa_flash_bwd_dkdv and
  * fa_flash_bwd_dq.  fa_flash_bwd_fused on an uncovered shape returns FA_ERR_UNSUPPORTED, with a
@@ -327,6 +337,21 @@ int fa_rotary_pair_bwd(int32_t dtype, int32_t B, int32_t H, int32_t L, int32_t D
  * (0 = healthy) and optionally clears it.  The reference has no counterpart:
  * its Triton kernels contain no waits (src/flag_attn/flash.py:325-489). */
 int fa_device_status(int32_t *out, int32_t clear);
+
+/* Self-test of that mechanism, for test suites: launches one 64-thread CTA that waits for at
+ * most `limit_cycles` SM clocks (1 .. 20,000,000, i.e. at most about 10 ms) on an mbarrier that
+ * nobody arrives at, then gives up the way every tensor-core kernel does: status word := 990,
+ * abort flag raised, normal return.  *left_flag (device int, may be NULL) is set to 1 when the
+ * wait was abandoned.  Until fa_device_status(.., clear = 1) the tensor-core kernels of later
+ * calls return without doing any work.  No counterpart in the reference. */
+int fa_debug_wait_probe(int64_t limit_cycles, int32_t *left_flag, void *stream);
+
+/* Kernel family used by the flash / piecewise entry points: 0 (default) = tcgen05 kernels where
+ * they cover the call (head_dim 64 / 128, no dropout, layouts a tensor map can express), the
+ * shape-generic mma.sync kernels elsewhere; 1 = shape-generic kernels only (what the tests use to
+ * cross-check the two families).  Process-wide; returns the previous value.  The environment
+ * variable FLAGATTN_B200_GENERIC=1 sets the initial value.  No counterpart in the reference. */
+int32_t fa_set_kernel_family(int32_t family);
 
 const char *fa_status_string(int status);
 /* Library build identification: "flagattn_b200 <n> sm_100a". */

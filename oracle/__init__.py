@@ -13,6 +13,7 @@ holds input seeds and outputs produced by importing the reference
 """
 from .flash import flash_attention  # noqa: F401
 from .piecewise import piecewise_attention, piecewise_attention_grad  # noqa: F401
-from .paged import paged_attention, paged_attention_gathered, cache_append  # noqa: F401
+from .paged import (paged_attention, paged_attention_gathered,  # noqa: F401
+                    paged_attention_same_precision, cache_append)  # noqa: F401
 from .dropout import dropout_mask, philox_uniform  # noqa: F401
 from .rotary import rotary, rotary_pair, rotary_pair_backward  # noqa: F401

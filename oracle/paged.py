@@ -39,8 +39,17 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, s
     return out
 
 
-def paged_attention_gathered(query, key_cache, value_cache, block_tables, context_lens, scale):
-    out = torch.empty_like(query)
+def _gather(cache, ids, ctx):
+    """(kv_heads, ctx, head) view of one sequence's tokens: blocks `ids` laid end to end."""
+    n_kv_heads, _, head_size = cache.shape[1:]
+    return cache.index_select(0, ids).permute(1, 0, 2, 3).reshape(n_kv_heads, -1, head_size)[:, :ctx]
+
+
+def paged_attention_gathered(query, key_cache, value_cache, block_tables, context_lens, scale,
+                             out_dtype=None):
+    """out_dtype=torch.float32 keeps the fp32 result unrounded (the reference rounds it to the cache
+    dtype, src/flag_attn/testing/paged.py:48): the fp32 side of the 2x tolerance rule."""
+    out = torch.empty_like(query, dtype=out_dtype or query.dtype)
     n_q_heads = query.shape[1]
     n_kv_heads, block_size, head_size = value_cache.shape[1:]
     group = n_q_heads // n_kv_heads
@@ -59,7 +68,28 @@ def paged_attention_gathered(query, key_cache, value_cache, block_tables, contex
         scores = torch.bmm(qi, keys.float().transpose(1, 2)) * scale
         probs = torch.softmax(scores, dim=-1)
         oi = torch.bmm(probs, values.float()).squeeze(1)
-        out[i].copy_(oi.to(values.dtype))
+        out[i].copy_(oi.to(out.dtype))
+    return out
+
+
+def paged_attention_same_precision(query, key_cache, value_cache, block_tables, context_lens, scale):
+    """The same-precision PyTorch path for paged decode, which the reference does not have (its test
+    is an allclose, tests/flag_attn/test_paged_attention.py:62): per sequence, the flash oracle of
+    src/flag_attn/testing/flash.py:5-70 with upcast=False on the single query token against the
+    densely gathered keys and values, i.e. matmuls in the cache dtype and an fp32 softmax.  With it
+    the reference's 2x rule (kernel error <= 2 x error of this path, both against fp32) applies to
+    paged_attention too."""
+    from .flash import flash_attention
+    out = torch.empty_like(query)
+    block_size = value_cache.shape[2]
+    lens = context_lens.cpu().tolist()
+    for i in range(query.shape[0]):
+        ctx = int(lens[i])
+        ids = block_tables[i, :(ctx + block_size - 1) // block_size].long()
+        keys, values = _gather(key_cache, ids, ctx), _gather(value_cache, ids, ctx)
+        o = flash_attention(query[i][None, :, None, :], keys[None], values[None], False,
+                            sm_scale=scale, upcast=False)
+        out[i].copy_(o[0, :, 0, :])
     return out
 
 

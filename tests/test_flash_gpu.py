@@ -7,6 +7,8 @@ import torch
 
 import flagattention_b200 as fa
 import oracle
+from flagattention_b200 import _C
+from flagattention_b200 import flash as fl
 from helpers import GOLDEN, assert_within_2x, make_qkv, max_diff
 
 pytestmark = pytest.mark.gpu
@@ -132,16 +134,14 @@ def test_empty_rows_give_zero_output_and_neg_inf_lse():
     assert torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
 
 
-def _three_runs(monkeypatch, two_kernels):
-    if two_kernels:
-        monkeypatch.setenv("FLAGATTN_B200_BWD_TWO_KERNELS", "1")
+def _three_runs(mode):
     q, k, v, do = make_qkv(2, 4, 2, 777, 901, 128, torch.bfloat16, "cuda", seed=11)
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
     outs = []
     for use_side in (False, False, True):
         stream = torch.cuda.Stream() if use_side else torch.cuda.current_stream()
         stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
+        with torch.cuda.stream(stream), fl.backward_mode(mode):
             o = fa.flash_attention(q, k, v, True)
             g = torch.autograd.grad(o, (q, k, v), do)
         stream.synchronize()
@@ -149,10 +149,10 @@ def _three_runs(monkeypatch, two_kernels):
     return outs
 
 
-def test_deterministic_and_stream_safe(monkeypatch):
+def test_deterministic_and_stream_safe():
     """Two runs, and a run on a side stream, give the same bits for o, dk, dv.  dq of the one-pass
     backward is a sum of fp32 reductions in arbitrary order: equal to within a 16-bit rounding step."""
-    outs = _three_runs(monkeypatch, two_kernels=False)
+    outs = _three_runs("one_pass")
     for other in outs[1:]:
         for i, (a, b) in enumerate(zip(outs[0], other)):
             if i == 1:   # dq
@@ -161,24 +161,44 @@ def test_deterministic_and_stream_safe(monkeypatch):
                 assert torch.equal(a, b)
 
 
-def test_two_kernel_backward_is_bitwise_deterministic(monkeypatch):
+def test_two_kernel_backward_is_bitwise_deterministic():
     """The dK/dV + dQ kernel pair uses no atomics: every output is bitwise reproducible."""
-    outs = _three_runs(monkeypatch, two_kernels=True)
+    outs = _three_runs("two_kernel")
     for other in outs[1:]:
         for a, b in zip(outs[0], other):
             assert torch.equal(a, b)
 
 
+def test_torch_determinism_switch_selects_the_atomics_free_backward():
+    """Under torch.use_deterministic_algorithms(True) the default ("auto") backward is the
+    dK/dV + dQ pair: the same bits as the explicit "two_kernel" mode, run after run."""
+    q, k, v, do = make_qkv(1, 4, 2, 600, 600, 128, torch.bfloat16, "cuda", seed=21)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = fa.flash_attention(q, k, v, True)
+    with fl.backward_mode("two_kernel"):
+        want = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+    before = torch.are_deterministic_algorithms_enabled()
+    try:
+        torch.use_deterministic_algorithms(True)
+        for _ in range(2):
+            got = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+            for a, b in zip(got, want):
+                assert torch.equal(a, b)
+    finally:
+        torch.use_deterministic_algorithms(before)
+
+
 @pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal", [(1, 4, 4, 1024, 1024, 128, True), (2, 4, 2, 500, 700, 64, True),
                                                   (1, 2, 2, 333, 1111, 128, False), (1, 2, 1, 1500, 300, 64, True)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_one_pass_backward_matches_two_kernel_backward(monkeypatch, B, Hq, Hk, M, N, D, causal, dtype):
+def test_one_pass_backward_matches_two_kernel_backward(B, Hq, Hk, M, N, D, causal, dtype):
     q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", seed=5 + M)
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
     o = fa.flash_attention(q, k, v, causal)
-    g1 = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
-    monkeypatch.setenv("FLAGATTN_B200_BWD_TWO_KERNELS", "1")
-    g2 = torch.autograd.grad(o, (q, k, v), do)
+    with fl.backward_mode("one_pass"):
+        g1 = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+    with fl.backward_mode("two_kernel"):
+        g2 = torch.autograd.grad(o, (q, k, v), do)
     for a, b in zip(g1, g2):
         scale = b.float().abs().max().item()
         assert (a.float() - b.float()).abs().max().item() <= 2 ** -6 * scale + 1e-6
@@ -220,8 +240,8 @@ def test_cfg1_shape_fp16_against_fp32_golden():
                                            (2, 4, 4, 4001, 4096, 64), (2, 4, 2, 4096, 4001, 128),
                                            (2, 4, 2, 10006, 10, 128)])
 @pytest.mark.parametrize("causal", [True, False])
-def test_generic_kernels_at_tensor_core_head_dims(B, Hq, Hk, M, N, D, causal, monkeypatch):
-    """head_dim 64/128 normally run on the tcgen05 kernels; FLAGATTN_B200_GENERIC=1 routes them to
+def test_generic_kernels_at_tensor_core_head_dims(B, Hq, Hk, M, N, D, causal):
+    """head_dim 64/128 normally run on the tcgen05 kernels; the kernel-family switch routes them to
     the shape-generic kernels, which must meet the same bar (and agree with the tcgen05 ones)."""
     dtype = torch.bfloat16 if causal else torch.float16
     q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 1.0, "BHTD", seed=M + D)
@@ -232,9 +252,9 @@ def test_generic_kernels_at_tensor_core_head_dims(B, Hq, Hk, M, N, D, causal, mo
     g_tor = torch.autograd.grad(o_tor, (q, k, v), do)
     results = {}
     for mode in ("1", "0"):
-        monkeypatch.setenv("FLAGATTN_B200_GENERIC", mode)
-        o, L, *_ = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)
-        g = torch.autograd.grad(o, (q, k, v), do)
+        with _C.kernel_family("generic" if mode == "1" else "auto"):
+            o, L, *_ = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)
+            g = torch.autograd.grad(o, (q, k, v), do)
         assert_within_2x(o, o_ref, o_tor, f"o generic={mode}")
         assert_within_2x(L, l_ref, l_tor, f"lse generic={mode}")
         for name, h, r, t in zip(("dq", "dk", "dv"), g, g_ref, g_tor):
@@ -243,6 +263,75 @@ def test_generic_kernels_at_tensor_core_head_dims(B, Hq, Hk, M, N, D, causal, mo
     for a, b_ in zip(results["0"], results["1"]):
         fin = torch.isfinite(a.float())
         assert max_diff(a[fin], b_[fin]) <= 4 * 2 ** -8 * max(1.0, a[fin].float().abs().max().item())
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("how", ["heads", "batch", "both"])
+@pytest.mark.parametrize("mode", ["one_pass", "two_kernel"])
+def test_broadcast_strides_of_k_and_v(D, how, mode):
+    """K and V given as broadcast views (stride 0 on a dimension longer than one: one KV head
+    expanded over the query heads, a prefix shared by the batch).  A tensor map cannot express
+    that, so these calls must leave the tcgen05 path and still give the oracle's result, forward
+    and backward (the gradient of an expanded view sums over the broadcast dimension)."""
+    B, H, M, N = 2, 4, 200, 264
+    dtype = torch.bfloat16
+    gen = torch.Generator().manual_seed(5 + D)
+    q = torch.randn((B, H, M, D), generator=gen).to(dtype).cuda().requires_grad_()
+    do = torch.randn((B, H, M, D), generator=gen).to(dtype).cuda()
+    base_shape = {"heads": (B, 1, N, D), "batch": (1, H, N, D), "both": (1, 1, N, D)}[how]
+    kb = torch.randn(base_shape, generator=gen).to(dtype).cuda().requires_grad_()
+    vb = torch.randn(base_shape, generator=gen).to(dtype).cuda().requires_grad_()
+    k, v = kb.expand(B, H, N, D), vb.expand(B, H, N, D)
+    assert 0 in k.stride()
+    with fl.backward_mode(mode):
+        o, L, *_ = fa.flash_attention(q, k, v, True, return_log_normalizer=True)
+        g = torch.autograd.grad(o, (q, kb, vb), do)
+    o_ref, l_ref, _ = oracle.flash_attention(q, k, v, True, return_log_normalizer=True, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, kb, vb), do)
+    o_tor, l_tor, _ = oracle.flash_attention(q, k, v, True, return_log_normalizer=True, upcast=False)
+    g_tor = torch.autograd.grad(o_tor, (q, kb, vb), do)
+    assert_within_2x(o, o_ref, o_tor, "o")
+    assert_within_2x(L, l_ref, l_tor, "lse")
+    for name, h, r, t in zip(("dq", "dk", "dv"), g, g_ref, g_tor):
+        assert_within_2x(h, r, t, name)
+    # and the same numbers as with K and V materialised (which do run on tcgen05)
+    o2 = fa.flash_attention(q, k.contiguous(), v.contiguous(), True)
+    assert max_diff(o, o2) <= 4 * 2 ** -8 * max(1.0, o2.float().abs().max().item())
+
+
+def test_a_wait_that_runs_out_poisons_the_status_word_and_the_context_survives():
+    """Every wait in the tensor-core kernels has a time limit.  fa_debug_wait_probe makes one run
+    out on purpose (an mbarrier nobody arrives at, limit about a millisecond): the kernel must
+    return normally, leave its code in the device status word, later tensor-core launches must do
+    nothing until the word is cleared, and after clearing everything works again."""
+    import ctypes
+    lib = _C.load()
+    out = ctypes.c_int32(-1)
+    assert lib.fa_device_status(ctypes.byref(out), 1) == 0 and out.value == 0
+    q, k, v, _ = make_qkv(1, 2, 2, 256, 256, 128, torch.bfloat16, "cuda", seed=31)
+    o_good = fa.flash_attention(q, k, v, True)
+    left = torch.zeros(1, dtype=torch.int32, device="cuda")
+    try:
+        st = lib.fa_debug_wait_probe(2_000_000, ctypes.c_void_p(left.data_ptr()),
+                                     _C.stream_ptr(q.device))
+        assert st == 0
+        torch.cuda.synchronize()                      # the kernel came back by itself
+        assert left.item() == 1                       # ... because the wait was abandoned
+        assert lib.fa_device_status(ctypes.byref(out), 0) == 0 and out.value == 990
+        # a poisoned word: the forward kernel returns at once and leaves its output untouched
+        shape = _C.flash_shape(q.dtype, 1, 2, 2, 256, 256, 128, True, 128 ** -0.5)
+        o = torch.full_like(q, 7.0)
+        lse = torch.full((1, 2, 256), 7.0, device="cuda")
+        ts = [_C.tensor4(x) for x in (q, k, v, o)]
+        st = lib.fa_flash_fwd(_C.byref(shape), *[_C.byref(t) for t in ts], _C.fptr(lse),
+                              _C.stream_ptr(q.device))
+        assert st == 0
+        torch.cuda.synchronize()
+        assert torch.all(o == 7.0) and torch.all(lse == 7.0)
+    finally:
+        assert lib.fa_device_status(ctypes.byref(out), 1) == 0
+    assert lib.fa_device_status(ctypes.byref(out), 0) == 0 and out.value == 0
+    assert torch.equal(fa.flash_attention(q, k, v, True), o_good)
 
 
 def test_device_status_word_is_clean():
@@ -296,17 +385,17 @@ def test_single_query_forward_fallbacks():
 
 
 @pytest.mark.parametrize("generic", ["1", "0"])
-def test_rows_without_visible_keys_are_exact_zeros_every_time(generic, monkeypatch):
+def test_rows_without_visible_keys_are_exact_zeros_every_time(generic):
     """M > N causal: CTAs whose rows see no key run no main-loop iteration.  Their output rows must
     be exact zeros (lse = -inf) on every run, whatever the freed memory they reuse holds (the
     shape-generic forward once let a late asynchronous copy of Q land in its staged output)."""
-    monkeypatch.setenv("FLAGATTN_B200_GENERIC", generic)
     B, Hq, Hk, M, N, D = 2, 4, 2, 10006, 10, 128
     q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, torch.bfloat16, "cuda", 1.0, "BHTD", seed=M + D)
     for rep in range(12):
         junk = torch.full((48 << 20,), float("nan") if rep % 2 else 3.0, device="cuda", dtype=torch.bfloat16)
         del junk
-        o, L, *_ = fa.flash_attention(q, k, v, True, return_log_normalizer=True)
+        with _C.kernel_family("generic" if generic == "1" else "auto"):
+            o, L, *_ = fa.flash_attention(q, k, v, True, return_log_normalizer=True)
         assert torch.count_nonzero(o[:, :, :M - N]).item() == 0
         assert torch.isinf(L[:, :, :M - N]).all() and (L[:, :, :M - N] < 0).all()
         assert torch.isfinite(o).all() and torch.isfinite(L[:, :, M - N:]).all()
@@ -324,13 +413,11 @@ def test_ragged_last_group_of_the_launch_order(B, Hq, Hk, M, N, D, causal):
     q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 1.0, "BHTD", seed=B + Hq + M)
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
     o = fa.flash_attention(q, k, v, causal)
-    grads = torch.autograd.grad(o, (q, k, v), do)
-    os.environ["FLAGATTN_B200_BWD_TWO_KERNELS"] = "1"
-    try:
-        o2 = fa.flash_attention(q, k, v, causal)
+    with fl.backward_mode("one_pass"):
+        grads = torch.autograd.grad(o, (q, k, v), do)
+    o2 = fa.flash_attention(q, k, v, causal)
+    with fl.backward_mode("two_kernel"):
         grads2 = torch.autograd.grad(o2, (q, k, v), do)
-    finally:
-        os.environ.pop("FLAGATTN_B200_BWD_TWO_KERNELS", None)
     G = Hq // Hk
     for b in range(B):
         for hk in range(Hk):

@@ -148,20 +148,20 @@ def test_rotary_host_checks_and_table_normalisation():
     assert abs(cos[3, 5].item() - math.cos(ang)) < 1e-6 and abs(sin[3, 5].item() - math.sin(ang)) < 1e-6
 
     good = [torch.zeros(10, 16) for _ in range(4)]
-    tabs, rows, stride = rotary._tables_ready(good, 16)
+    tabs, rows, stride = rotary._tables_ready(good, 16, torch.device("cpu"))
     assert rows == 10 and stride == 16 and all(a is b for a, b in zip(tabs, good))
     wide = [torch.zeros(10, 64) for _ in range(4)]               # more columns than D / 2: read in place
-    tabs, rows, stride = rotary._tables_ready(wide, 16)
+    tabs, rows, stride = rotary._tables_ready(wide, 16, torch.device("cpu"))
     assert stride == 64 and all(a is b for a, b in zip(tabs, wide))
     odd = [torch.zeros(10, 35)[:, :16] for _ in range(4)]         # row stride 35: re-packed
-    tabs, rows, stride = rotary._tables_ready(odd, 16)
+    tabs, rows, stride = rotary._tables_ready(odd, 16, torch.device("cpu"))
     assert stride == 16 and all(t.is_contiguous() for t in tabs)
     with pytest.raises(AssertionError):
-        rotary._tables_ready([torch.zeros(10, 16, dtype=torch.float64)] * 4, 16)
+        rotary._tables_ready([torch.zeros(10, 16, dtype=torch.float64)] * 4, 16, torch.device("cpu"))
     with pytest.raises(AssertionError):
-        rotary._tables_ready([torch.zeros(10, 8)] * 4, 16)        # fewer than D / 2 columns
+        rotary._tables_ready([torch.zeros(10, 8)] * 4, 16, torch.device("cpu"))        # fewer than D / 2 columns
     with pytest.raises(AssertionError):
-        rotary._tables_ready([torch.zeros(10, 16)] * 3 + [torch.zeros(9, 16)], 16)
+        rotary._tables_ready([torch.zeros(10, 16)] * 3 + [torch.zeros(9, 16)], 16, torch.device("cpu"))
 
     pos, _, stride_b = rotary._positions_ready(torch.arange(7, dtype=torch.int32), 3, 7, "cpu")
     assert pos.dtype == torch.int64 and pos.shape == (1, 7) and stride_b == 0      # one row for the batch
@@ -177,3 +177,70 @@ def test_rotary_host_checks_and_table_normalisation():
     assert list(inspect.signature(fa.rotary_pair).parameters) == [
         "x", "cos1", "sin1", "cos2", "sin2", "positions", "interleaved"]
     assert hasattr(fa.testing, "rotary_pair")
+
+
+def test_operands_on_the_wrong_device_raise_before_any_launch():
+    """Host tensors where device tensors are expected raise AssertionError; nothing is launched
+    (a kernel handed a host pointer would fault on the GPU)."""
+    from flagattention_b200 import rotary
+    x = torch.zeros(1, 2, 8, 32, dtype=torch.float16)
+    tabs = fa.rotary_tables(8, 32)                              # default device: CPU
+    with pytest.raises(AssertionError):
+        fa.rotary_pair(x, *tabs, *tabs)                         # x itself is not a CUDA tensor
+    with pytest.raises(AssertionError):
+        rotary._tables_ready(list(tabs) * 2, 16, torch.device("cuda", 0))   # tables left on the CPU
+    q = torch.zeros(1, 2, 8, 32, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        fa.piecewise_attention(q, q, q, q, q, 4)
+    with pytest.raises(AssertionError):
+        fa.flash_attention(q, q, q)
+    with pytest.raises(AssertionError):
+        fa.paged_attention(torch.zeros(2, 8, 32, dtype=torch.float16),
+                           torch.zeros(4, 8, 16, 32, dtype=torch.float16),
+                           torch.zeros(4, 8, 16, 32, dtype=torch.float16),
+                           torch.ones(2, dtype=torch.int32), torch.zeros(2, 1, dtype=torch.int32),
+                           1.0, 16)
+    meta_q = torch.zeros(2, 8, 32, dtype=torch.float16, device="meta")
+    with pytest.raises(AssertionError):                         # query elsewhere than its tables
+        fa.paged_attention(meta_q, torch.zeros(4, 8, 16, 32, dtype=torch.float16, device="meta"),
+                           torch.zeros(4, 8, 16, 32, dtype=torch.float16, device="meta"),
+                           torch.ones(2, dtype=torch.int32), torch.zeros(2, 1, dtype=torch.int32),
+                           1.0, 16)
+    with pytest.raises(AssertionError):
+        fa.reshape_and_cache(torch.zeros(2, 8, 32, dtype=torch.float16),
+                             torch.zeros(2, 8, 32, dtype=torch.float16),
+                             torch.zeros(4, 8, 16, 32, dtype=torch.float16),
+                             torch.zeros(4, 8, 16, 32, dtype=torch.float16),
+                             torch.zeros(2, dtype=torch.int64))
+
+
+def test_backward_mode_switch():
+    """Which backward kernels run is an API, not an environment variable: explicit modes, a context
+    manager, and "auto" following torch's determinism switch."""
+    from flagattention_b200 import flash as fl
+    assert fl.get_backward_mode() == "auto"
+    assert fl.use_one_pass_backward()
+    with fl.backward_mode("two_kernel"):
+        assert fl.get_backward_mode() == "two_kernel" and not fl.use_one_pass_backward()
+        with fl.backward_mode("one_pass"):
+            assert fl.use_one_pass_backward()
+        assert not fl.use_one_pass_backward()
+    assert fl.get_backward_mode() == "auto"
+    before = torch.are_deterministic_algorithms_enabled()
+    try:
+        torch.use_deterministic_algorithms(True)
+        assert not fl.use_one_pass_backward()
+        with fl.backward_mode("one_pass"):
+            assert fl.use_one_pass_backward()
+    finally:
+        torch.use_deterministic_algorithms(before)
+    with pytest.raises(AssertionError):
+        fl.set_backward_mode("fast")
+
+
+def test_kernel_family_switch(built_lib):
+    lib = _C.load()
+    assert lib.fa_set_kernel_family(0) == 0
+    with _C.kernel_family("generic"):
+        assert lib.fa_set_kernel_family(1) == 1
+    assert lib.fa_set_kernel_family(0) == 0

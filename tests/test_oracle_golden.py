@@ -102,6 +102,29 @@ def test_paged_oracle_matches_reference(idx, impl):
     assert max_diff(o, c["out"]) <= 1e-6 + 2 ** -11 * c["out"].float().abs().max().item()
 
 
+@pytest.mark.parametrize("idx", range(len(PAGED["cases"])))
+def test_paged_same_precision_path_against_reference(idx):
+    """The same-precision PyTorch path of paged decode (the flash oracle with upcast=False on
+    gathered keys / values): on fp32 copies of a fixture it IS the fp32 computation, so it must
+    reproduce the reference's stored output; in the cache dtype it stays within 16-bit rounding."""
+    c = PAGED["cases"][idx]
+    args32 = (c["q"].float(), c["key_cache"].float(), c["value_cache"].float(), c["block_tables"],
+              c["context_lens"], c["scale"])
+    o32 = oracle.paged_attention_same_precision(*args32)
+    scale = c["out"].float().abs().max().item()
+    assert max_diff(o32, c["out"]) <= 1e-6 + 2 ** -11 * scale
+    unrounded = oracle.paged_attention_gathered(*args32, out_dtype=torch.float32)
+    assert unrounded.dtype == torch.float32 and max_diff(unrounded, o32) <= 1e-6
+    if c["q"].dtype == torch.bfloat16 or torch.cuda.is_available():
+        return   # fp16 matmuls on CPU are not available in every torch build
+    try:
+        o16 = oracle.paged_attention_same_precision(c["q"], c["key_cache"], c["value_cache"],
+                                                    c["block_tables"], c["context_lens"], c["scale"])
+    except RuntimeError:
+        return
+    assert max_diff(o16, c["out"]) <= 2 ** -7 * scale + 1e-4
+
+
 # ---- dropout random stream: oracle/dropout.py against the reference's mask kernel ----------------
 def _philox_golden():
     return torch.load(os.path.join(GOLDEN, "philox.pt"))

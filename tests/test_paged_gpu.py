@@ -9,7 +9,7 @@ import torch
 import flagattention_b200 as fa
 import oracle
 from flagattention_b200 import _C
-from helpers import GOLDEN, max_diff
+from helpers import GOLDEN, assert_within_2x, max_diff
 
 pytestmark = pytest.mark.gpu
 NUM_BLOCKS = 1000
@@ -35,6 +35,11 @@ def _check(q, kc, vc, lens, bt, scale, max_len, num_splits=0):
     ref = oracle.paged_attention_gathered(q, kc, vc, bt, lens, scale)
     assert out.shape == q.shape and out.dtype == q.dtype
     assert torch.allclose(out, ref, atol=2e-3, rtol=1e-5), f"max diff {max_diff(out, ref):.3e}"
+    # and the 2x rule of the dense operators: error against unrounded fp32 at most twice that of
+    # the same-precision PyTorch path on densely gathered keys / values
+    ref32 = oracle.paged_attention_gathered(q, kc, vc, bt, lens, scale, out_dtype=torch.float32)
+    same = oracle.paged_attention_same_precision(q, kc, vc, bt, lens, scale)
+    assert_within_2x(out, ref32, same, "paged out")
     return out
 
 
@@ -129,14 +134,22 @@ def test_block_table_indexing_is_bit_exact():
 
 
 def test_unused_table_entries_are_never_read():
-    """Entries past ceil(context_len / block_size) may hold garbage ids (here: far out of range)."""
+    """Entries past ceil(context_len / block_size) may hold anything.  Here they name a valid block
+    whose keys and values are NaN: a kernel that read one of them would return NaN, a failed
+    assertion instead of an out-of-range access."""
     q, kc, vc, lens, bt, scale, mx = _make(6, 16, 2, 128, 16, 700, torch.int32, seed=33)
+    poison_id = NUM_BLOCKS - 1
+    bt = bt.clamp(max=poison_id - 1)                     # no live entry names the poisoned block
+    kc, vc = kc.clone(), vc.clone()
+    kc[poison_id], vc[poison_id] = float("nan"), float("nan")
     used = (lens.long() + 15) // 16
     cols = torch.arange(bt.shape[1], device="cuda")[None, :]
-    poisoned = torch.where(cols < used[:, None], bt, torch.full_like(bt, 2 ** 30))
+    poisoned = torch.where(cols < used[:, None], bt, torch.full_like(bt, poison_id))
+    assert (poisoned == poison_id).any()
     for splits in (0, 1, 4):
         a = fa.paged_attention(q, kc, vc, lens, bt, scale, mx, splits)
         b = fa.paged_attention(q, kc, vc, lens, poisoned, scale, mx, splits)
+        assert torch.isfinite(b.float()).all()
         assert torch.equal(a, b)
 
 

@@ -7,6 +7,7 @@ import torch
 
 import flagattention_b200 as fa
 import oracle
+from flagattention_b200 import _C
 from helpers import GOLDEN, assert_within_2x
 
 pytestmark = pytest.mark.gpu
@@ -88,8 +89,8 @@ def test_golden_fixtures_on_gpu():
 @pytest.mark.parametrize("B,H,M,N,D", [(2, 4, 512, 612, 128), (2, 4, 1024, 1034, 64), (1, 3, 700, 700, 128),
                                        (1, 2, 1500, 1300, 64)])
 @pytest.mark.parametrize("causal", [True, False])
-def test_generic_kernels_at_tensor_core_head_dims(B, H, M, N, D, causal, monkeypatch):
-    """head_dim 64/128 normally run on the tcgen05 kernels; FLAGATTN_B200_GENERIC=1 routes them to the
+def test_generic_kernels_at_tensor_core_head_dims(B, H, M, N, D, causal):
+    """head_dim 64/128 normally run on the tcgen05 kernels; the kernel-family switch routes them to the
     shape-generic kernels, which must meet the same bar."""
     dtype = torch.bfloat16 if causal else torch.float16
     q1, k1, q2, k2, v, do = _inputs(B, H, M, N, D, dtype, "BHTD", 1.0, seed=M + D)
@@ -100,9 +101,9 @@ def test_generic_kernels_at_tensor_core_head_dims(B, H, M, N, D, causal, monkeyp
     o_tor = oracle.piecewise_attention(*ins, w, causal, upcast=False)
     g_tor = torch.autograd.grad(o_tor, ins, do)
     for mode in ("1", "0"):
-        monkeypatch.setenv("FLAGATTN_B200_GENERIC", mode)
-        o = fa.piecewise_attention(*ins, w, causal=causal)
-        g = torch.autograd.grad(o, ins, do)
+        with _C.kernel_family("generic" if mode == "1" else "auto"):
+            o = fa.piecewise_attention(*ins, w, causal=causal)
+            g = torch.autograd.grad(o, ins, do)
         assert_within_2x(o, o_ref, o_tor, f"o generic={mode}")
         for name, h, r, t in zip(("dq1", "dk1", "dq2", "dk2", "dv"), g, g_ref, g_tor):
             assert_within_2x(h, r, t, f"{name} generic={mode}")

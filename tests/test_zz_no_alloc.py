@@ -5,13 +5,16 @@ HBM for its KV-cache pool, or a decode loop that is not allowed to enter the CUD
 them the split-KV scratch lives in a fixed array inside the library.  This test drives that entry
 point through the C ABI, twice in a row with different inputs (the array keeps the first call's
 contents, which must not leak into the second result), and compares each output with the ordinary
-entry points working on a torch-allocated workspace.  The file name makes pytest collect it last.
+entry points working on a torch-allocated workspace and with the oracle.  A third call repeats the
+first problem's layout with shorter contexts, so that partition slots the first call filled are
+left unwritten: the reducer must not read them.  The file name makes pytest collect it last.
 """
 import ctypes
 
 import pytest
 import torch
 
+import oracle
 from flagattention_b200 import _C
 
 pytestmark = pytest.mark.gpu
@@ -19,10 +22,12 @@ pytestmark = pytest.mark.gpu
 SCRATCH_BYTES = 17039360   # FA_PAGED_NOALLOC_SCRATCH_BYTES in include/flagattn_b200.h
 
 
-def _problem(seed, num_seqs, q_heads, kv_heads, head, block, max_len, partition, table_dtype):
+def _problem(seed, num_seqs, q_heads, kv_heads, head, block, max_len, partition, table_dtype,
+             len_cap=None):
     gen = torch.Generator().manual_seed(seed)
-    lens = torch.randint(1, max_len, (num_seqs,), generator=gen, dtype=torch.int32)
-    lens[0] = max_len
+    lens = torch.randint(1, len_cap or max_len, (num_seqs,), generator=gen, dtype=torch.int32)
+    if len_cap is None:
+        lens[0] = max_len
     nb = 400
     scale = head ** -0.5
     q = ((torch.rand((num_seqs, q_heads, head), generator=gen) * 2 - 1) * scale).half().cuda()
@@ -41,7 +46,7 @@ def _problem(seed, num_seqs, q_heads, kv_heads, head, block, max_len, partition,
     a.kv_stride_b, a.kv_stride_h, a.kv_stride_t = kc.stride()[:3]
     a.context_lens, a.block_tables, a.bt_stride_s = lens.data_ptr(), bt.data_ptr(), bt.stride(0)
     a.out, a.o_stride_s, a.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
-    keep = (q, kc, vc, bt, lens)          # keeps the device buffers alive
+    keep = (q, kc, vc, bt, lens, scale)   # keeps the device buffers alive
     return a, out, keep
 
 
@@ -72,14 +77,21 @@ def test_noalloc_matches_workspace_path_twice_in_a_row():
     problems = [
         _problem(101, 6, 32, 8, 128, 16, 3000, 512, torch.int32),
         _problem(202, 9, 16, 16, 64, 32, 1700, 256, torch.int64),   # other shape, other layout of the array
+        _problem(101, 6, 32, 8, 128, 16, 3000, 512, torch.int32),
+        # the layout of the call before, contexts of at most 600 tokens: the slots of partitions
+        # 2..5 still hold that call's numbers and must stay unread
+        _problem(404, 6, 32, 8, 128, 16, 3000, 512, torch.int32, len_cap=600),
     ]
-    for a, out, _keep in problems:
+    for a, out, keep in problems:
         out.fill_(float("nan"))
         assert lib.fa_paged_attention_noalloc(ctypes.byref(a), stream) == 0
         torch.cuda.synchronize()
         want = _with_workspace(a, out)
         assert torch.isfinite(out.float()).all()
         assert torch.allclose(out, want, atol=2e-3, rtol=1e-5), (out.float() - want.float()).abs().max()
+        q, kc, vc, bt, lens, scale = keep
+        ref = oracle.paged_attention_gathered(q, kc, vc, bt, lens, scale)
+        assert torch.allclose(out, ref, atol=2e-3, rtol=1e-5), (out.float() - ref.float()).abs().max()
 
 
 def test_noalloc_rejects_what_does_not_fit_and_one_pass_mode():

@@ -18,9 +18,20 @@ static bool fused_covered(const fa_flash_shape *s) {
          (s->D == 64 || s->D == 128) && s->dropout_p == 0.f;
 }
 
-static int64_t fused_workspace_bytes(const fa_flash_shape *s) {
+// fp32 dq accumulator (B, H, Mpad, D), then 16 bytes that hold the kernel's work-item counter
+static int64_t fused_dq_acc_bytes(const fa_flash_shape *s) {
   const int64_t mpad = ((int64_t)s->M + 127) / 128 * 128;
   return (int64_t)s->B * s->H * mpad * s->D * 4;
+}
+static int64_t fused_workspace_bytes(const fa_flash_shape *s) { return fused_dq_acc_bytes(s) + 16; }
+
+// one persistent CTA per SM
+static int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+    return 0;
+  return n;
 }
 
 template <typename T, int D>
@@ -51,6 +62,7 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
   fp.dq_acc = workspace;
   fp.Mpad = (s->M + 127) / 128 * 128;
+  fp.sched = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(workspace) + fused_dq_acc_bytes(s));
   // stages: 1 = zero-fill of the workspace, 2 = the kernel, 4 = scale + convert the workspace to dq
   if ((stages & 1) &&
       cudaMemsetAsync(workspace, 0, (size_t)fused_workspace_bytes(s), stream) != cudaSuccess)
@@ -59,7 +71,13 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
     // the CTAs of a (batch, kv head) pair share its Q and dO tiles and its slice of the dq workspace
     p.num_blocks = (s->N + C::BN - 1) / C::BN;
     p.group_size = cta_group_size((int64_t)(s->H / s->Hk) * s->M * D * 8, s->B * s->Hk);
-    dim3 grid((unsigned)((int64_t)p.num_blocks * s->Hk * s->B), 1, 1);
+    const int64_t items = (int64_t)p.num_blocks * s->Hk * s->B;
+    const int sms = sm_count();
+    if (items > 0x7fffffff) return FA_ERR_TOO_LARGE;
+    if (sms <= 0) return FA_ERR_LAUNCH;
+    fp.num_items = (int)items;
+    // persistent: a CTA takes item `blockIdx.x`, then items handed out by the counter
+    dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
     kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, mdk, mdv, fp);
     FA_CHECK_LAUNCH();
   }

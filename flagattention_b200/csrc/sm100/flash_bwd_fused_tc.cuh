@@ -48,23 +48,28 @@ struct FusedBwdCfg {
   static constexpr int kQuarter = (D / 16) * 2048;
   static constexpr int kStage = kPD + kPdBytes;
   static constexpr int kBars = kStage + 2 * kQuarter;
-  static constexpr int kMisc = kBars + 24 * 8;
-  static constexpr int kStats = kMisc + 16;            // -lse*log2e [128] | -delta [128] of a tile
+  static constexpr int kMisc = kBars + 32 * 8;         // tmem base, abort flag, ring of work items
+  static constexpr int kStats = kMisc + 32;            // -lse*log2e [128] | -delta [128] of a tile
   static constexpr int kTotal = kStats + 2 * 128 * 4 + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColA = 0, kColQ = 128, kColDK = 256, kColDV = 256 + D;
+  static_assert(kPdBytes >= kTile, "dK is staged in the P^T / dS^T tile");
   static_assert(kTotal <= 232448, "shared memory budget");
 };
 
 enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB_DO_FREE = 7,
                 FB_S_FULL = 9, FB_S_LOADED = 10, FB_DP_FULL = 11, FB_DP_LOADED = 12,
                 FB_PT_FULL = 13, FB_PT_FREE = 14, FB_DS_FULL = 15, FB_DS_FREE = 16,
-                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19, FB_LSE_FULL = 20, FB_DLT_FULL = 21, FB_V_FULL = 22 };
+                FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19, FB_LSE_FULL = 20, FB_DLT_FULL = 21,
+                FB_V_FULL = 22, FB_DV_STAGED = 23, FB_DK_STAGED = 24, FB_PD_STORED = 25,
+                FB_ITEM_FULL = 26 /* .. 29 */ };
 
 struct FusedBwdParams {
   BwdTcParams base;
   float *dq_acc;   // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
   int Mpad;        // M rounded up to a multiple of 128
+  unsigned *sched; // work-item counter, zeroed before the launch (see the kernel)
+  int num_items;   // key blocks x (batch, kv head) pairs
 };
 
 // fp32 add of `bytes` contiguous bytes of shared memory into global memory, done by the copy
@@ -104,20 +109,6 @@ __device__ __forceinline__ bool red_warps_all(bool ok) {
   return out != 0;
 }
 
-// barrier 2 with a vote: the 16 element-wise warps (512 threads)
-__device__ __forceinline__ bool ew_warps_all(bool ok) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %1, 0;\n\t"
-      "bar.red.and.pred q, 2, 512, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}\n"
-      : "=r"(out)
-      : "r"((uint32_t)ok)
-      : "memory");
-  return out != 0;
-}
-
 // one box of a (d, l, h, b) tensor map, shared memory -> global memory; rows past the tensor's
 // end are dropped by the copy engine
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t smem_src, int c0, int c1,
@@ -133,6 +124,20 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t sm
 // lane slice), 22 statistics
 constexpr int kFusedThreads = kBwdThreads + 5 * 32;   // 736
 
+// One work item = one block of 128 keys of one (batch, kv head) pair: its query-tile range.
+struct FusedItem {
+  int n0, hk, b, mt_lo, mt_hi, T_tiles;
+};
+
+// PERSISTENT: the grid is one CTA per SM.  A CTA works through items (key block, pair) in the
+// order of grouped_cta(): its first item is its block index, every further one comes from a
+// global counter (`sched`, zero at launch), fetched one item ahead by the producer thread and
+// handed to the other warps through a four-slot ring in shared memory.  Barriers, TMEM and the
+// operand rings are set up once per CTA and their phases simply keep counting across items, so
+// the tail of an item overlaps the head of the next: while the element-wise warps convert dV and
+// dK of item i (dV into the shared memory of V, dK into the P^T / dS^T tile, both dead by then)
+// and the copy engine stores them, the producer already loads Q, dO, K and V of item i + 1 and the
+// tensor pipe computes its first score tile.
 template <typename T, int D>
 __global__ void __launch_bounds__(kFusedThreads, 1)
     flash_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -150,30 +155,42 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   auto bar = [&](int i) { return smem + C::kBars + i * 8; };
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + C::kMisc);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + C::kMisc + 8);
+  volatile int *item_ring = reinterpret_cast<volatile int *>(smem_gen + C::kMisc + 16);   // 4 slots
   const AbortCtx actx{abort_flag, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const CtaCoord cta = grouped_cta(blockIdx.x, p.num_blocks, p.B * p.Hk, p.group_size);
-  const int nb = cta.blk, hk = cta.pair % p.Hk, b = cta.pair / p.Hk;
   const int G = p.H / p.Hk;
-  const int n0 = nb * BN;
   const int p_seq = p.N - p.M;
   const int num_m_tiles = (p.M + BM - 1) / BM;
-  int mt_lo = 0;
-  if (p.causal) mt_lo = max(0, n0 - p_seq) / BM;
-  int mt_hi = num_m_tiles;
-  if (p.mode == 1) {  // query tiles that hold a near pair
-    const int lim = p.w - p_seq + n0 + BN - 1;
-    mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
-  } else if (p.mode == 2) {  // query tiles that hold a far pair
-    const int lim = p.w - p_seq + n0 - (BM - 1);
-    mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
-  }
-  const int tiles = max(0, mt_hi - mt_lo);
-  const int T_tiles = tiles * G;
+  const int total = fp.num_items;
+
+  auto decode = [&](int w) -> FusedItem {
+    const CtaCoord cta = grouped_cta((unsigned)w, p.num_blocks, p.B * p.Hk, p.group_size);
+    FusedItem it;
+    it.n0 = cta.blk * BN, it.hk = cta.pair % p.Hk, it.b = cta.pair / p.Hk;
+    int mt_lo = 0;
+    if (p.causal) mt_lo = max(0, it.n0 - p_seq) / BM;
+    int mt_hi = num_m_tiles;
+    if (p.mode == 1) {  // query tiles that hold a near pair
+      const int lim = p.w - p_seq + it.n0 + BN - 1;
+      mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+    } else if (p.mode == 2) {  // query tiles that hold a far pair
+      const int lim = p.w - p_seq + it.n0 - (BM - 1);
+      mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+    }
+    it.mt_lo = mt_lo, it.mt_hi = mt_hi;
+    it.T_tiles = max(0, mt_hi - mt_lo) * G;
+    return it;
+  };
+  // the id of this CTA's `ic`-th item, as published by the producer thread (>= total: no more)
+  auto ring_item = [&](int ic, int where) -> int {
+    if (!mbar_wait(bar(FB_ITEM_FULL + (ic & 3)), (ic >> 2) & 1, actx, where)) return -1;
+    return item_ring[ic & 3];
+  };
 
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
 
+  const FusedItem first = decode(blockIdx.x);   // the grid never exceeds the number of items
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar(FB_KV_FULL), 1);   // K
@@ -199,30 +216,36 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     mbar_init(bar(FB_DONE), 1);
     mbar_init(bar(FB_LSE_FULL), 1);
     mbar_init(bar(FB_DLT_FULL), 1);
+    mbar_init(bar(FB_DV_STAGED), kEwWarps);
+    mbar_init(bar(FB_DK_STAGED), kEwWarps);
+    mbar_init(bar(FB_PD_STORED), 1);
+    for (int s = 0; s < 4; ++s) mbar_init(bar(FB_ITEM_FULL + s), 1);
     fence_barrier_init();
+    item_ring[0] = (int)blockIdx.x;
+    mbar_arrive(bar(FB_ITEM_FULL + 0));
     // The loads of the first tile go out right here, before the TMEM allocation and the CTA-wide
     // barrier below, so that their latency (the first bytes of K, V, Q, dO come from HBM) runs
     // under the rest of the set-up.  K and Q first: S^T of the first tile needs only those.
-    if (T_tiles > 0) {
-      const int h0 = hk * G, m00 = mt_lo * BM;
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_v);
-      tma_prefetch_desc(&map_do);
-      tma_prefetch_desc(&map_dk);
-      tma_prefetch_desc(&map_dv);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_dk);
+    tma_prefetch_desc(&map_dv);
+    if (first.T_tiles > 0) {
+      const int h0 = first.hk * G, m00 = first.mt_lo * BM;
       mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, n0, hk, b);
+        tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, first.n0, first.hk, first.b);
       mbar_expect_tx(bar(FB_Q_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kQ0 + s * BM * 128, &map_q, bar(FB_Q_FULL), s * 64, m00, h0, b);
+        tma_load_4d(smem + C::kQ0 + s * BM * 128, &map_q, bar(FB_Q_FULL), s * 64, m00, h0, first.b);
       mbar_expect_tx(bar(FB_V_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, n0, hk, b);
+        tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, first.n0, first.hk, first.b);
       mbar_expect_tx(bar(FB_DO_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kDO0 + s * BM * 128, &map_do, bar(FB_DO_FULL), s * 64, m00, h0, b);
+        tma_load_4d(smem + C::kDO0 + s * BM * 128, &map_do, bar(FB_DO_FULL), s * 64, m00, h0, first.b);
     }
   }
   if (warp == 0) {
@@ -236,46 +259,136 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 
   if (warp == 0) {
     // ------------------------------ producer -----------------------------------
-    if (lane == 0 && T_tiles > 0) {
-      // (tile 0 was requested during set-up)
-      int issued_q = 1, issued_do = 1;
+    if (lane == 0) {
       bool ok = true;
-      int sq = 0, phq = 1, sd = 0, phd = 1;   // slot and the "free" parity to wait for
-      int h = hk * G, mt = mt_lo;
-      for (int t = 0; t < T_tiles; ++t) {
-        const int m0 = mt * BM;
-        if (t > 0) {
-          ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 711);
-          if (!ok) break;
-          mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
+      int sq = 0, phq = 1, sd = 0, phd = 1;   // ring slot and the "free" parity to wait for
+      int inflight_q = 0, inflight_do = 0;    // loads requested (for the drain after an abort)
+      int real = 0;                           // items with tiles handled so far
+      bool pending = false;                   // dV / dK of the previous such item not stored yet
+      int pn0 = 0, phk = 0, pb = 0;           // its coordinates
+      auto load_q = [&](const FusedItem &it, int h, int mt) {
+        mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
+        for (int s = 0; s < KSUB; ++s)
+          tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
+                      s * 64, mt * BM, h, it.b);
+        ++inflight_q;
+      };
+      auto load_do = [&](const FusedItem &it, int h, int mt) {
+        mbar_expect_tx(bar(FB_DO_FULL + sd), C::kTile);
+        for (int s = 0; s < KSUB; ++s)
+          tma_load_4d(smem + C::kDO0 + sd * C::kTile + s * BM * 128, &map_do, bar(FB_DO_FULL + sd),
+                      s * 64, mt * BM, h, it.b);
+        ++inflight_do;
+      };
+      // dV then dK of the previous item leave through the copy engine as soon as the element-wise
+      // warps have staged them; `between` runs after the dV store has been requested
+      auto store_dv = [&]() -> bool {
+        if (!mbar_wait(bar(FB_DV_STAGED), (real - 1) & 1, actx, 721)) return false;
+        if (!p.dv_accumulate) {
+#pragma unroll
           for (int s = 0; s < KSUB; ++s)
-            tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
-                        s * 64, m0, h, b);
-          ++issued_q;
-          ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 712);
-          if (!ok) break;
-          mbar_expect_tx(bar(FB_DO_FULL + sd), C::kTile);
-          for (int s = 0; s < KSUB; ++s)
-            tma_load_4d(smem + C::kDO0 + sd * C::kTile + s * BM * 128, &map_do, bar(FB_DO_FULL + sd),
-                        s * 64, m0, h, b);
-          ++issued_do;
+            tma_store_4d(&map_dv, smem + C::kV + s * BN * 128, s * 64, pn0, phk, pb);
+          bulk_commit();
         }
-        if (++sq == NQ) sq = 0, phq ^= 1;
-        if (++sd == NDO) sd = 0, phd ^= 1;
-        if (++mt == mt_hi) mt = mt_lo, ++h;
+        return true;
+      };
+      auto store_dk = [&]() -> bool {
+        if (!mbar_wait(bar(FB_DK_STAGED), (real - 1) & 1, actx, 722)) return false;
+#pragma unroll
+        for (int s = 0; s < KSUB; ++s)
+          tma_store_4d(&map_dk, smem + C::kPD + s * BN * 128, s * 64, pn0, phk, pb);
+        bulk_commit();
+        return true;
+      };
+      int w = blockIdx.x, ic = 0;
+      while (w < total && ok) {
+        // fetch the id of the next item now, so that its latency hides behind this item
+        const int w_next = (int)gridDim.x + (int)atomicAdd(fp.sched, 1u);
+        item_ring[(ic + 1) & 3] = w_next;
+        mbar_arrive(bar(FB_ITEM_FULL + ((ic + 1) & 3)));
+        const FusedItem it = decode(w);
+        if (it.T_tiles > 0) {
+          int h = it.hk * G, mt = it.mt_lo;
+          const bool preissued = (ic == 0);   // tile 0, K and V of the first item: see set-up
+          if (preissued) {
+            inflight_q = inflight_do = 1;
+          } else {
+            ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 711);
+            if (!ok) break;
+            load_q(it, h, mt);
+            ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 712);
+            if (!ok) break;
+            load_do(it, h, mt);
+            if (pending) {
+              ok = store_dv();
+              // K is free once every product of the previous item has completed
+              if (ok) ok = mbar_wait(bar(FB_DONE), (real - 1) & 1, actx, 723);
+              if (!ok) break;
+            }
+            mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
+            for (int s = 0; s < KSUB; ++s)
+              tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, it.n0, it.hk, it.b);
+            if (pending) {
+              ok = store_dk();
+              if (!ok) break;
+              bulk_wait_read_1();            // the dV store has read the shared memory of V
+            }
+            mbar_expect_tx(bar(FB_V_FULL), C::kTile);
+            for (int s = 0; s < KSUB; ++s)
+              tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, it.n0, it.hk, it.b);
+            if (pending) {
+              bulk_wait_read_all();          // the dK store has read the P^T / dS^T tile
+              mbar_arrive(bar(FB_PD_STORED));
+            }
+          }
+          pending = true, pn0 = it.n0, phk = it.hk, pb = it.b;
+          ++real;
+          if (++sq == NQ) sq = 0, phq ^= 1;
+          if (++sd == NDO) sd = 0, phd ^= 1;
+          if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
+          for (int t = 1; t < it.T_tiles; ++t) {
+            ok = mbar_wait(bar(FB_Q_FREE + sq), phq, actx, 713);
+            if (!ok) break;
+            load_q(it, h, mt);
+            ok = mbar_wait(bar(FB_DO_FREE + sd), phd, actx, 714);
+            if (!ok) break;
+            load_do(it, h, mt);
+            if (++sq == NQ) sq = 0, phq ^= 1;
+            if (++sd == NDO) sd = 0, phd ^= 1;
+            if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
+          }
+        } else if (pending) {
+          // an item without tiles: nothing to load, so the previous item's stores go out now
+          ok = store_dv();
+          if (ok) ok = store_dk();
+          if (!ok) break;
+          bulk_wait_read_all();
+          mbar_arrive(bar(FB_PD_STORED));
+          pending = false;
+        }
+        w = w_next, ++ic;
       }
+      if (ok && pending) {
+        ok = store_dv();
+        if (ok) ok = store_dk();
+      }
+      bulk_wait_read_all();   // shared memory must outlive the copy engine's reads
       if (!ok) {
         // let copies already in flight land before the CTA gives its shared memory back
         const long long t0 = clock64();
-        for (int i = max(0, issued_q - NQ); i < issued_q; ++i)
+        for (int i = max(0, inflight_q - NQ); i < inflight_q; ++i)
           while (!mbar_try_wait(bar(FB_Q_FULL + i % NQ), (i / NQ) & 1) && clock64() - t0 < 2000000) {}
-        for (int i = max(0, issued_do - NDO); i < issued_do; ++i)
+        for (int i = max(0, inflight_do - NDO); i < inflight_do; ++i)
           while (!mbar_try_wait(bar(FB_DO_FULL + i % NDO), (i / NDO) & 1) && clock64() - t0 < 2000000) {}
+        if (real > 0) {
+          while (!mbar_try_wait(bar(FB_KV_FULL), (real - 1) & 1) && clock64() - t0 < 2000000) {}
+          while (!mbar_try_wait(bar(FB_V_FULL), (real - 1) & 1) && clock64() - t0 < 2000000) {}
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------
-    if (lane == 0 && T_tiles > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = instr_desc_f16(BN, BM, TcElem<T>::kFormat, 0, 0);   // S^T, dP^T
       constexpr uint32_t idesc_acc = instr_desc_f16(BN, D, TcElem<T>::kFormat, 0, 1);  // dV, dK
       constexpr uint32_t idesc_dq = instr_desc_f16(BM, D, TcElem<T>::kFormat, 1, 1);   // dQ
@@ -288,7 +401,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       const uint32_t do_mn_lo = smem_desc_lo(smem + C::kDO0, BM * 128);
       const uint32_t pd_k_lo = smem_desc_lo(smem + C::kPD, 0);            // P^T / dS^T, K-major A
       const uint32_t pd_mn_lo = smem_desc_lo(smem + C::kPD, BN * 128);    // dS, MN-major A of dQ
-      bool ok = mbar_wait(bar(FB_KV_FULL), 0, actx, 811);
       // S^T = K Q^T into the score columns
       auto issue_s = [&](int sq, int phq) -> bool {
         if (!mbar_wait(bar(FB_Q_FULL + sq), phq, actx, 812)) return false;
@@ -302,81 +414,98 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         mma_commit(bar(FB_S_FULL));
         return true;
       };
-      if (ok) ok = issue_s(0, 0);
+      bool ok = true;
       int sq = 0, phq = 0, sd = 0, phd = 0;
-      for (int t = 0; t < T_tiles && ok; ++t) {
-        int nsq = sq + 1, nphq = phq;
-        if (nsq == NQ) nsq = 0, nphq ^= 1;
-        const uint32_t acc = t > 0 ? 1u : 0u;
-        const uint32_t par = t & 1;
-        // dP^T(t) = V dO^T over S^T(t), once every element-wise warp holds S^T(t) in registers
-        ok = mbar_wait(bar(FB_S_LOADED), par, actx, 813);
-        if (ok && t == 0) ok = mbar_wait(bar(FB_V_FULL), 0, actx, 820);
-        if (ok) ok = mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 814);
-        if (!ok) break;
-        tc_fence_after();
-        {
-          const uint32_t b_lo = do_k_lo + sd * kTile16;
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
-            mma_ss_lo(tmem + C::kColA, v_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
-          }
-          mma_commit(bar(FB_DP_FULL));
+      int real = 0;            // items with tiles so far
+      uint32_t gt = 0;         // tiles so far, over all items: the phase of every per-tile barrier
+      for (int ic = 0; ok; ++ic) {
+        const int w = ring_item(ic, 801);
+        if (w < 0 || w >= total) break;
+        const FusedItem it = decode(w);
+        if (it.T_tiles == 0) continue;
+        ok = mbar_wait(bar(FB_KV_FULL), real & 1, actx, 811);
+        // the score columns still hold dP^T of the previous item's last tile until the
+        // element-wise warps have it in registers
+        if (ok && gt > 0) ok = mbar_wait(bar(FB_DP_LOADED), (gt - 1) & 1, actx, 821);
+        if (ok) {
+          tc_fence_after();
+          ok = issue_s(sq, phq);
         }
-        // dV += P^T(t) dO(t), P^T from shared memory
-        ok = mbar_wait(bar(FB_PT_FULL), par, actx, 815);
-        if (!ok) break;
-        tc_fence_after();
-        {
-          const uint32_t b_lo = do_mn_lo + sd * kTile16;
-#pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk) {
-            const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
-            mma_ss_lo(tmem + C::kColDV, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
-                      kk > 0 ? 1u : acc);
-          }
-          mma_commit(bar(FB_DO_FREE + sd));
-          mma_commit(bar(FB_PT_FREE));
-        }
-        // S^T(t+1), once every element-wise warp holds dP^T(t) in registers
-        if (t + 1 < T_tiles) {
-          ok = mbar_wait(bar(FB_DP_LOADED), par, actx, 816);
+        for (int t = 0; t < it.T_tiles && ok; ++t, ++gt) {
+          int nsq = sq + 1, nphq = phq;
+          if (nsq == NQ) nsq = 0, nphq ^= 1;
+          const uint32_t acc = t > 0 ? 1u : 0u;
+          const uint32_t par = gt & 1;
+          // dP^T(t) = V dO^T over S^T(t), once every element-wise warp holds S^T(t) in registers
+          ok = mbar_wait(bar(FB_S_LOADED), par, actx, 813);
+          if (ok && t == 0) ok = mbar_wait(bar(FB_V_FULL), real & 1, actx, 820);
+          if (ok) ok = mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 814);
           if (!ok) break;
           tc_fence_after();
-          ok = issue_s(nsq, nphq);
-          if (!ok) break;
-        }
-        // dQ(t) = dS(t) K, a fresh accumulator: the read-out of dQ(t-1) must be over
-        ok = mbar_wait(bar(FB_DS_FULL), par, actx, 817);
-        if (ok && t > 0) ok = mbar_wait(bar(FB_DQ_FREE), (t - 1) & 1, actx, 818);
-        if (!ok) break;
-        tc_fence_after();
+          {
+            const uint32_t b_lo = do_k_lo + sd * kTile16;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint32_t off16 = (kk * 16 * 128) >> 4;
-          mma_ss_lo(tmem + C::kColQ, pd_mn_lo + off16, k_mn_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
-        }
-        mma_commit(bar(FB_DQ_FULL));
-        // dK += dS^T(t) Q(t)
-        {
-          const uint32_t b_lo = q_mn_lo + sq * kTile16;
-#pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk) {
-            const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
-            mma_ss_lo(tmem + C::kColDK, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
-                      kk > 0 ? 1u : acc);
+            for (int k = 0; k < D / 16; ++k) {
+              const uint32_t off16 = ((k / 4) * 128 * 128 + (k % 4) * 32) >> 4;
+              mma_ss_lo(tmem + C::kColA, v_lo + off16, b_lo + off16, idesc_s, k > 0 ? 1u : 0u);
+            }
+            mma_commit(bar(FB_DP_FULL));
           }
-          mma_commit(bar(FB_Q_FREE + sq));
-          mma_commit(bar(FB_DS_FREE));
+          // dV += P^T(t) dO(t), P^T from shared memory
+          ok = mbar_wait(bar(FB_PT_FULL), par, actx, 815);
+          if (!ok) break;
+          tc_fence_after();
+          {
+            const uint32_t b_lo = do_mn_lo + sd * kTile16;
+#pragma unroll
+            for (int kk = 0; kk < BM / 16; ++kk) {
+              const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
+              mma_ss_lo(tmem + C::kColDV, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
+                        kk > 0 ? 1u : acc);
+            }
+            mma_commit(bar(FB_DO_FREE + sd));
+            mma_commit(bar(FB_PT_FREE));
+          }
+          // S^T(t+1), once every element-wise warp holds dP^T(t) in registers
+          if (t + 1 < it.T_tiles) {
+            ok = mbar_wait(bar(FB_DP_LOADED), par, actx, 816);
+            if (!ok) break;
+            tc_fence_after();
+            ok = issue_s(nsq, nphq);
+            if (!ok) break;
+          }
+          // dQ(t) = dS(t) K, a fresh accumulator: the read-out of the previous dQ must be over
+          ok = mbar_wait(bar(FB_DS_FULL), par, actx, 817);
+          if (ok && gt > 0) ok = mbar_wait(bar(FB_DQ_FREE), (gt - 1) & 1, actx, 818);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            const uint32_t off16 = (kk * 16 * 128) >> 4;
+            mma_ss_lo(tmem + C::kColQ, pd_mn_lo + off16, k_mn_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
+          }
+          mma_commit(bar(FB_DQ_FULL));
+          // dK += dS^T(t) Q(t)
+          {
+            const uint32_t b_lo = q_mn_lo + sq * kTile16;
+#pragma unroll
+            for (int kk = 0; kk < BM / 16; ++kk) {
+              const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
+              mma_ss_lo(tmem + C::kColDK, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
+                        kk > 0 ? 1u : acc);
+            }
+            mma_commit(bar(FB_Q_FREE + sq));
+            mma_commit(bar(FB_DS_FREE));
+          }
+          sq = nsq, phq = nphq;
+          if (++sd == NDO) sd = 0, phd ^= 1;
         }
-        sq = nsq, phq = nphq;
-        if (++sd == NDO) sd = 0, phd ^= 1;
-      }
-      if (ok) {
+        if (!ok) break;
         mma_commit(bar(FB_DONE));
-        mbar_wait(bar(FB_DONE), 0, actx, 819);
+        ++real;
       }
+      // the last commit's arrive must land before this CTA's shared memory is given back
+      if (ok && real > 0) mbar_wait(bar(FB_DONE), (real - 1) & 1, actx, 819);
     }
   } else if (warp == 2 + kEwWarps + 4) {
     // ------------------------------ statistics warp ----------------------------
@@ -385,33 +514,39 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     // all its 32 query columns; fetching them lane by lane and shuffling costs 64 shuffles per
     // thread and tile in a load/store queue that is already the busiest unit).  Queries past M
     // get lse = +inf, which makes their P exactly zero.  One buffer each: lse(t) may be written
-    // once phase 1 of tile t - 1 is over, delta(t) once phase 2 of tile t - 1 is.
+    // once phase 1 of the tile before is over, delta(t) once its phase 2 is.
     float4 *lse_s = reinterpret_cast<float4 *>(smem_gen + C::kStats);
     float4 *dlt_s = lse_s + 32;
-    int h = hk * G, mt = mt_lo;
     bool ok = true;
-    for (int t = 0; t < T_tiles; ++t) {
-      const int m = mt * BM + lane * 4;
-      const int64_t li = ((int64_t)b * p.H + h) * p.M + m;
-      if (++mt == mt_hi) mt = mt_lo, ++h;
-      float l[4], d[4];
+    uint32_t gt = 0;
+    for (int ic = 0; ok; ++ic) {
+      const int w = ring_item(ic, 950);
+      if (w < 0 || w >= total) break;
+      const FusedItem it = decode(w);
+      int h = it.hk * G, mt = it.mt_lo;
+      for (int t = 0; t < it.T_tiles; ++t, ++gt) {
+        const int m = mt * BM + lane * 4;
+        const int64_t li = ((int64_t)it.b * p.H + h) * p.M + m;
+        if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
+        float l[4], d[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        l[j] = m + j < p.M ? -p.lse[li + j] * kLog2e : -INFINITY;
-        d[j] = m + j < p.M ? -p.delta[li + j] : 0.f;
+        for (int j = 0; j < 4; ++j) {
+          l[j] = m + j < p.M ? -p.lse[li + j] * kLog2e : -INFINITY;
+          d[j] = m + j < p.M ? -p.delta[li + j] : 0.f;
+        }
+        if (gt > 0) ok = mbar_wait(bar(FB_PT_FULL), (gt - 1) & 1, actx, 951);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        lse_s[lane] = make_float4(l[0], l[1], l[2], l[3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_LSE_FULL));
+        if (gt > 0) ok = mbar_wait(bar(FB_DS_FULL), (gt - 1) & 1, actx, 952);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        dlt_s[lane] = make_float4(d[0], d[1], d[2], d[3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_DLT_FULL));
       }
-      if (t > 0) ok = mbar_wait(bar(FB_PT_FULL), (t - 1) & 1, actx, 951);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      lse_s[lane] = make_float4(l[0], l[1], l[2], l[3]);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_LSE_FULL));
-      if (t > 0) ok = mbar_wait(bar(FB_DS_FULL), (t - 1) & 1, actx, 952);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      dlt_s[lane] = make_float4(d[0], d[1], d[2], d[3]);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_DLT_FULL));
     }
   } else if (warp >= 2 + kEwWarps) {
     // ------------------------------ dQ reduction warps --------------------------
@@ -428,45 +563,52 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
     const bool issuer = (warp == 2 + kEwWarps) && lane == 0;
     constexpr int QC = D / 4;                 // columns per quarter
-    int h = hk * G, mt = mt_lo;
     int buf = 0;
     bool ok = true;
-    for (int t = 0; t < T_tiles; ++t) {
-      // the tile's block of the workspace: D / 4 runs of (128 queries x 4 columns), contiguous
-      float *dst = fp.dq_acc + (((int64_t)b * p.H + h) * (fp.Mpad / BM) + mt) * (int64_t)(BM * D);
-      if (++mt == mt_hi) mt = mt_lo, ++h;
-      // every wait is bounded, so all four warps reach the vote; they leave together or not at all
-      ok = red_warps_all(mbar_wait(bar(FB_DQ_FULL), t & 1, actx, 921));
-      if (!ok) break;
-      tc_fence_after();
+    uint32_t gt = 0;
+    for (int ic = 0; ok; ++ic) {
+      // every wait is bounded, so all four warps reach each vote; they leave together or not at all
+      const int w = ring_item(ic, 920);
+      if (!red_warps_all(w >= 0)) break;
+      if (w >= total) break;
+      const FusedItem it = decode(w);
+      int h = it.hk * G, mt = it.mt_lo;
+      for (int t = 0; t < it.T_tiles; ++t, ++gt) {
+        // the tile's block of the workspace: D / 4 runs of (128 queries x 4 columns), contiguous
+        float *dst = fp.dq_acc + (((int64_t)it.b * p.H + h) * (fp.Mpad / BM) + mt) * (int64_t)(BM * D);
+        if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
+        ok = red_warps_all(mbar_wait(bar(FB_DQ_FULL), gt & 1, actx, 921));
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
-        uint32_t qr[QC];
-        if (QC == 32) tmem_ld32(tlane + C::kColQ + qd * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
-        else tmem_ld16(tlane + C::kColQ + qd * QC, qr);
-        tmem_wait_ld();
-        if (qd == 3) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(FB_DQ_FREE));   // dQ(t+1) may overwrite the columns
-        }
-        // the copy engine must have read what this buffer held two quarters ago
-        if (issuer) bulk_wait_read_1();
-        red_warps_sync();
-        uint8_t *stage = smem_gen + C::kStage + buf * C::kQuarter + row * 16;
+        for (int qd = 0; qd < 4; ++qd) {
+          uint32_t qr[QC];
+          if (QC == 32) tmem_ld32(tlane + C::kColQ + qd * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
+          else tmem_ld16(tlane + C::kColQ + qd * QC, qr);
+          tmem_wait_ld();
+          if (qd == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(FB_DQ_FREE));   // the next dQ may overwrite the columns
+          }
+          // the copy engine must have read what this buffer held two quarters ago
+          if (issuer) bulk_wait_read_1();
+          red_warps_sync();
+          uint8_t *stage = smem_gen + C::kStage + buf * C::kQuarter + row * 16;
 #pragma unroll
-        for (int g = 0; g < QC / 4; ++g)
-          *reinterpret_cast<uint4 *>(stage + g * 2048) =
-              make_uint4(qr[4 * g], qr[4 * g + 1], qr[4 * g + 2], qr[4 * g + 3]);
-        fence_proxy_async_smem();
-        red_warps_sync();
-        if (issuer) {
-          // one contiguous run per quarter; rows past M hold zeros and land in padding
-          bulk_reduce_add_f32(dst + qd * (C::kQuarter / 4), smem + C::kStage + buf * C::kQuarter,
-                              C::kQuarter);
-          bulk_commit();
+          for (int g = 0; g < QC / 4; ++g)
+            *reinterpret_cast<uint4 *>(stage + g * 2048) =
+                make_uint4(qr[4 * g], qr[4 * g + 1], qr[4 * g + 2], qr[4 * g + 3]);
+          fence_proxy_async_smem();
+          red_warps_sync();
+          if (issuer) {
+            // one contiguous run per quarter; rows past M hold zeros and land in padding
+            bulk_reduce_add_f32(dst + qd * (C::kQuarter / 4), smem + C::kStage + buf * C::kQuarter,
+                                C::kQuarter);
+            bulk_commit();
+          }
+          buf ^= 1;
         }
-        buf ^= 1;
       }
     }
     if (issuer) bulk_wait_read_all();   // shared memory must outlive the copy engine's reads
@@ -475,10 +617,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     const int ew = warp - 2;
     const int slice = warp & 3, cg = ew >> 2;       // TMEM lane slice, 32-column group
     const int row = slice * 32 + lane;              // accumulator row of this thread
-    const int key = n0 + row;
     const uint32_t tlane = tmem + ((uint32_t)(slice * 32) << 16);
     const float qk_scale = p.sm_scale * kLog2e;
-    const bool key_ok = key < p.N;
     // this thread's 64 bytes of a PD row: sub-tile cg / 2, 16-byte chunks (cg & 1) * 4 .. + 3
     uint8_t *pd_row = smem_gen + C::kPD + (cg >> 1) * (128 * 128) + row * 128;
     const int pd_chunk0 = (cg & 1) * 4, pd_xor = row & 7;
@@ -488,142 +628,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         *reinterpret_cast<uint4 *>(pd_row + (((pd_chunk0 + j) ^ pd_xor) << 4)) =
             make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
     };
-    bool ok = true;
-
     // -lse * log2(e) / -delta of this thread's 32 query columns, as staged by the statistics warp
     const float4 *lse_s = reinterpret_cast<const float4 *>(smem_gen + C::kStats) + cg * 8;
     const float4 *dlt_s = lse_s + 32;
-    int mt = mt_lo;   // query tile of the current tile
-
-    for (int t = 0; t < T_tiles; ++t) {
-      const int m0 = mt * BM;
-      if (++mt == mt_hi) mt = mt_lo;
-
-      // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
-      ok = mbar_wait(bar(FB_LSE_FULL), t & 1, actx, 910);
-      if (ok) ok = mbar_wait(bar(FB_S_FULL), t & 1, actx, 911);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      float pv[32];
-      uint32_t sr[32];
-      tmem_ld32(tlane + C::kColA + cg * 32, sr);
-      // while the load is in flight: the masks
-      // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
-      // masking at all; the others mask with one unsigned range check per element:
-      // column c is visible iff cmin <= c < cmin + cwidth.
-      bool interior = (n0 + BN <= p.N) && (!p.causal || m0 + p_seq >= n0 + BN - 1);
-      if (p.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
-      if (p.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
-      int cmin = 0, cmax = 32;
-      if (p.causal) cmin = max(cmin, key - p_seq - m0 - cg * 32);
-      if (p.mode) {
-        const int cnear = p.w + key - p_seq - m0 - cg * 32;  // columns below it are near pairs
-        if (p.mode == 1) cmax = min(cmax, cnear);
-        else cmin = max(cmin, cnear);
-      }
-      if (!key_ok) cmin = 32;
-      const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
-      {
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(FB_S_LOADED));   // dP^T(t) may overwrite S^T(t)
-        // packed fp32 pairs: one FMA per two elements
-        const uint64_t scale2 = f2_pack(qk_scale, qk_scale);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 l4 = lse_s[i];
-          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[4 * i]), __uint_as_float(sr[4 * i + 1])), scale2,
-                           f2_pack(l4.x, l4.y)),
-                    pv[4 * i], pv[4 * i + 1]);
-          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[4 * i + 2]), __uint_as_float(sr[4 * i + 3])),
-                           scale2, f2_pack(l4.z, l4.w)),
-                    pv[4 * i + 2], pv[4 * i + 3]);
-        }
-      }
-      if (!interior) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c)
-          pv[c] = ((unsigned)(c - cmin) < cwidth) ? pv[c] : -INFINITY;  // exp2(-inf) = 0
-      }
-      {
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          pv[c] = ex2(pv[c]);
-          pv[c + 1] = ex2(pv[c + 1]);
-          pk[c >> 1] = TcElem<T>::pack(pv[c], pv[c + 1]);
-        }
-        // PD still holds dS^T(t-1) until dQ(t-1) and dK(t-1) have read it
-        if (t > 0) ok = mbar_wait(bar(FB_DS_FREE), (t - 1) & 1, actx, 912);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        store_pd(pk);
-      }
-      // ---- phase 2: dS^T = P^T * (dP^T - delta) -> PD ----
-      // Its operands are there by now (dP^T(t) was issued as soon as S^T(t) had been read), so the
-      // first TMEM load goes out before the proxy fence of phase 1 and hides behind it.
-      ok = mbar_wait(bar(FB_DLT_FULL), t & 1, actx, 909);
-      if (ok) ok = mbar_wait(bar(FB_DP_FULL), t & 1, actx, 913);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t sr0[16];
-      tmem_ld16(tlane + C::kColA + cg * 32, sr0);
-      fence_proxy_async_smem();   // the MMA reads PD through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
-      {
-        uint32_t pk[16];
-        // P * (dP - delta) of 16 columns, two elements per instruction
-        auto half_ds = [&](int hf, const uint32_t (&sr)[16]) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 d4 = dlt_s[hf * 4 + i];
-            const int c = 4 * i;
-            float e0, e1, e2, e3;
-            f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c], pv[hf * 16 + c + 1]),
-                             f2_add(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])),
-                                    f2_pack(d4.x, d4.y))),
-                      e0, e1);
-            f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c + 2], pv[hf * 16 + c + 3]),
-                             f2_add(f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])),
-                                    f2_pack(d4.z, d4.w))),
-                      e2, e3);
-            pk[hf * 8 + 2 * i] = TcElem<T>::pack(e0, e1);
-            pk[hf * 8 + 2 * i + 1] = TcElem<T>::pack(e2, e3);
-          }
-        };
-        tmem_wait_ld();            // first 16 columns (requested before the fence above)
-        half_ds(0, sr0);
-        {
-          uint32_t sr1[16];
-          tmem_ld16(tlane + C::kColA + cg * 32 + 16, sr1);
-          tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // S^T(t+1) may overwrite dP^T(t)
-          half_ds(1, sr1);
-        }
-        // PD still holds P^T(t) until dV(t) has read it
-        ok = mbar_wait(bar(FB_PT_FREE), t & 1, actx, 914);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        store_pd(pk);
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(FB_DS_FULL));
-    }
-
-    // ---- write-out of dV and dK: warp (slice, cg) owns columns cg * D / 4 .. of its 32 rows ----
-    // dV is final once its last product has been committed (the PT_FREE wait that ended the loop),
-    // so it is converted and handed to the copy engine while dQ and dK of the last tile still run
-    // on the tensor cores; dK follows after the last commit.  The tiles are staged in the shared
-    // memory of V and K (both dead by then) in the layout of their own loads, and leave as bulk
-    // tensor stores, which also drop the rows past N.  Two cases keep per-thread global stores:
-    // a dV that is added to (the second launch of a piecewise backward) and a CTA without tiles.
+    // write-out of dV and dK: warp (slice, cg) owns columns cg * D / 4 .. of its 32 rows
     constexpr int QC = D / 4;
     const int col0 = cg * QC;
     auto load_cols = [&](uint32_t col_base, uint32_t (&ov)[QC]) {
@@ -638,6 +646,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           TcElem<T>::pack(__uint_as_float(ov[4]) * scale, __uint_as_float(ov[5]) * scale),
           TcElem<T>::pack(__uint_as_float(ov[6]) * scale, __uint_as_float(ov[7]) * scale));
     };
+    // a 128 x D 16-bit tile in the layout of a TMA box (128-byte rows, 128-byte swizzle)
     auto stage = [&](int region, const uint32_t (&ov)[QC], float scale) {
       uint8_t *base = smem_gen + region + (col0 / 64) * (128 * 128) + row * 128;
       const int ch0 = (col0 % 64) / 8;
@@ -645,70 +654,203 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       for (int j = 0; j < QC / 8; ++j)
         *reinterpret_cast<uint4 *>(base + (((ch0 + j) ^ (row & 7)) << 4)) = pack8(ov + 8 * j, scale);
     };
-    auto direct = [&](void *out, const Strides &so, uint32_t (&ov)[QC], float scale, bool add) {
-      if (!key_ok) return;
-      T *orow = row_ptr_mut<T>(out, so, b, hk, key) + col0;
+    bool ok = true;
+    int real = 0;
+    uint32_t gt = 0;
+
+    for (int ic = 0; ok; ++ic) {
+      const int w = ring_item(ic, 900);
+      ok = __all_sync(0xffffffffu, w >= 0);
+      if (!ok || w >= total) break;
+      const FusedItem it = decode(w);
+      const int n0 = it.n0, key = n0 + row;
+      const bool key_ok = key < p.N;
+      auto direct = [&](void *out, const Strides &so, uint32_t (&ov)[QC], float scale, bool add) {
+        if (!key_ok) return;
+        T *orow = row_ptr_mut<T>(out, so, it.b, it.hk, key) + col0;
 #pragma unroll
-      for (int j = 0; j < QC / 8; ++j) {
-        if (add) {
-          const uint4 old = *reinterpret_cast<const uint4 *>(orow + j * 8);
-          const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+        for (int j = 0; j < QC / 8; ++j) {
+          if (add) {
+            const uint4 old = *reinterpret_cast<const uint4 *>(orow + j * 8);
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
-          for (int e2 = 0; e2 < 4; ++e2) {
-            const float2 f = TcElem<T>::unpack(ow[e2]);
-            ov[8 * j + 2 * e2] = __float_as_uint(__uint_as_float(ov[8 * j + 2 * e2]) + f.x);
-            ov[8 * j + 2 * e2 + 1] = __float_as_uint(__uint_as_float(ov[8 * j + 2 * e2 + 1]) + f.y);
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const float2 f = TcElem<T>::unpack(ow[e2]);
+              ov[8 * j + 2 * e2] = __float_as_uint(__uint_as_float(ov[8 * j + 2 * e2]) + f.x);
+              ov[8 * j + 2 * e2 + 1] = __float_as_uint(__uint_as_float(ov[8 * j + 2 * e2 + 1]) + f.y);
+            }
+          }
+          *reinterpret_cast<uint4 *>(orow + j * 8) = pack8(ov + 8 * j, scale);
+        }
+      };
+      if (it.T_tiles == 0) {
+        // no query sees these keys: their gradients are zero (dV untouched where it is added to)
+        uint32_t ov[QC];
+#pragma unroll
+        for (int i = 0; i < QC; ++i) ov[i] = 0u;
+        direct(p.dk, p.sdk, ov, 1.f, false);
+        if (!p.dv_accumulate) direct(p.dv, p.sdv, ov, 1.f, false);
+        continue;
+      }
+      int mt = it.mt_lo;   // query tile of the current tile
+
+      for (int t = 0; t < it.T_tiles; ++t, ++gt) {
+        const int m0 = mt * BM;
+        if (++mt == it.mt_hi) mt = it.mt_lo;
+
+        // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
+        ok = mbar_wait(bar(FB_LSE_FULL), gt & 1, actx, 910);
+        if (ok) ok = mbar_wait(bar(FB_S_FULL), gt & 1, actx, 911);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        float pv[32];
+        uint32_t sr[32];
+        tmem_ld32(tlane + C::kColA + cg * 32, sr);
+        // while the load is in flight: the masks
+        // Tiles away from every boundary (sequence end, causal diagonal, piecewise threshold) need no
+        // masking at all; the others mask with one unsigned range check per element:
+        // column c is visible iff cmin <= c < cmin + cwidth.
+        bool interior = (n0 + BN <= p.N) && (!p.causal || m0 + p_seq >= n0 + BN - 1);
+        if (p.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
+        if (p.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
+        int cmin = 0, cmax = 32;
+        if (p.causal) cmin = max(cmin, key - p_seq - m0 - cg * 32);
+        if (p.mode) {
+          const int cnear = p.w + key - p_seq - m0 - cg * 32;  // columns below it are near pairs
+          if (p.mode == 1) cmax = min(cmax, cnear);
+          else cmin = max(cmin, cnear);
+        }
+        if (!key_ok) cmin = 32;
+        const unsigned cwidth = (unsigned)max(cmax - cmin, 0);
+        {
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(FB_S_LOADED));   // dP^T(t) may overwrite S^T(t)
+          // packed fp32 pairs: one FMA per two elements
+          const uint64_t scale2 = f2_pack(qk_scale, qk_scale);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 l4 = lse_s[i];
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[4 * i]), __uint_as_float(sr[4 * i + 1])), scale2,
+                             f2_pack(l4.x, l4.y)),
+                      pv[4 * i], pv[4 * i + 1]);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[4 * i + 2]), __uint_as_float(sr[4 * i + 3])),
+                             scale2, f2_pack(l4.z, l4.w)),
+                      pv[4 * i + 2], pv[4 * i + 3]);
           }
         }
-        *reinterpret_cast<uint4 *>(orow + j * 8) = pack8(ov + 8 * j, scale);
+        if (!interior) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            pv[c] = ((unsigned)(c - cmin) < cwidth) ? pv[c] : -INFINITY;  // exp2(-inf) = 0
+        }
+        {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            pv[c] = ex2(pv[c]);
+            pv[c + 1] = ex2(pv[c + 1]);
+            pk[c >> 1] = TcElem<T>::pack(pv[c], pv[c + 1]);
+          }
+          // PD still holds dS^T of the tile before until its dQ and dK products have read it, and,
+          // at the first tile of an item, the staged dK of the item before until it is stored
+          if (gt > 0) ok = mbar_wait(bar(FB_DS_FREE), (gt - 1) & 1, actx, 912);
+          if (ok && t == 0 && real > 0) ok = mbar_wait(bar(FB_PD_STORED), (real - 1) & 1, actx, 917);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          store_pd(pk);
+        }
+        // ---- phase 2: dS^T = P^T * (dP^T - delta) -> PD ----
+        // Its operands are there by now (dP^T(t) was issued as soon as S^T(t) had been read), so the
+        // first TMEM load goes out before the proxy fence of phase 1 and hides behind it.
+        ok = mbar_wait(bar(FB_DLT_FULL), gt & 1, actx, 909);
+        if (ok) ok = mbar_wait(bar(FB_DP_FULL), gt & 1, actx, 913);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr0[16];
+        tmem_ld16(tlane + C::kColA + cg * 32, sr0);
+        fence_proxy_async_smem();   // the MMA reads PD through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
+        {
+          uint32_t pk[16];
+          // P * (dP - delta) of 16 columns, two elements per instruction
+          auto half_ds = [&](int hf, const uint32_t (&sr)[16]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 d4 = dlt_s[hf * 4 + i];
+              const int c = 4 * i;
+              float e0, e1, e2, e3;
+              f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c], pv[hf * 16 + c + 1]),
+                               f2_add(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])),
+                                      f2_pack(d4.x, d4.y))),
+                        e0, e1);
+              f2_unpack(f2_mul(f2_pack(pv[hf * 16 + c + 2], pv[hf * 16 + c + 3]),
+                               f2_add(f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])),
+                                      f2_pack(d4.z, d4.w))),
+                        e2, e3);
+              pk[hf * 8 + 2 * i] = TcElem<T>::pack(e0, e1);
+              pk[hf * 8 + 2 * i + 1] = TcElem<T>::pack(e2, e3);
+            }
+          };
+          tmem_wait_ld();            // first 16 columns (requested before the fence above)
+          half_ds(0, sr0);
+          {
+            uint32_t sr1[16];
+            tmem_ld16(tlane + C::kColA + cg * 32 + 16, sr1);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // the next S^T may overwrite dP^T(t)
+            half_ds(1, sr1);
+          }
+          // PD still holds P^T(t) until dV(t) has read it
+          ok = mbar_wait(bar(FB_PT_FREE), gt & 1, actx, 914);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          store_pd(pk);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_DS_FULL));
       }
-    };
-    const bool elected = ew == 0 && lane == 0;
-    if (T_tiles > 0) {
-      // every element-wise warp runs both votes below, whatever happened to its own waits
-      uint32_t ov[QC];
-      const bool bulk_dv = !p.dv_accumulate;
-      if (ok) {
+      if (!ok) break;
+
+      // ---- write-out of dV and dK of this item ----
+      // dV is final once its last product has been committed (the PT_FREE wait that ended the loop),
+      // so it is converted and staged while dQ and dK of the last tile still run on the tensor
+      // cores; dK follows after the last commit.  dV is staged in the shared memory of V and dK in
+      // the P^T / dS^T tile (both dead by then) in the layout of an operand load, and the producer
+      // thread sends them off as bulk tensor stores, which also drop the rows past N.  A dV that is
+      // added to (the second launch of a piecewise backward) keeps per-thread global stores.
+      {
+        uint32_t ov[QC];
         tc_fence_after();
         load_cols(C::kColDV, ov);
-        if (bulk_dv) {
+        if (!p.dv_accumulate) {
           stage(C::kV, ov, 1.f);
           fence_proxy_async_smem();
         } else {
           direct(p.dv, p.sdv, ov, 1.f, true);
         }
-      }
-      ok = ew_warps_all(ok);
-      if (ok && bulk_dv && elected) {
-#pragma unroll
-        for (int s = 0; s < KSUB; ++s)
-          tma_store_4d(&map_dv, smem + C::kV + s * BN * 128, s * 64, n0, hk, b);
-        bulk_commit();
-      }
-      if (ok) ok = mbar_wait(bar(FB_DONE), 0, actx, 916);
-      ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_DV_STAGED));
+        ok = mbar_wait(bar(FB_DONE), real & 1, actx, 916);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         tc_fence_after();
         load_cols(C::kColDK, ov);
-        stage(C::kK, ov, p.sm_scale);
+        stage(C::kPD, ov, p.sm_scale);
         fence_proxy_async_smem();
+        // the accumulator columns are free for the next item once every warp has read them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(FB_DK_STAGED));
       }
-      ok = ew_warps_all(ok);
-      if (elected) {
-        if (ok) {
-#pragma unroll
-          for (int s = 0; s < KSUB; ++s)
-            tma_store_4d(&map_dk, smem + C::kK + s * BN * 128, s * 64, n0, hk, b);
-          bulk_commit();
-        }
-        bulk_wait_read_all();   // shared memory must outlive the copy engine's reads
-      }
-    } else if (ok) {
-      uint32_t ov[QC];
-#pragma unroll
-      for (int i = 0; i < QC; ++i) ov[i] = 0u;
-      direct(p.dk, p.sdk, ov, 1.f, false);
-      if (!p.dv_accumulate) direct(p.dv, p.sdv, ov, 1.f, false);
+      ++real;
     }
   }
 

@@ -6,7 +6,8 @@ collective on the data path: each rank computes its shard, and one all_gather re
 outputs only where a consumer wants the full tensor.
 
 The exception is a sequence too long for one GPU: ring_flash_attention shards the SEQUENCE over
-the ranks and passes key / value shards round a ring (forward only).
+the ranks and passes key / value shards round a ring, forward and backward (the gradients of a
+shard travel round the ring with it).
 """
 import torch
 

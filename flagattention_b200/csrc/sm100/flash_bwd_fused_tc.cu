@@ -1,5 +1,7 @@
 // Launcher and C entry points of the one-pass tcgen05 flash_attention backward.
 #include <cstdlib>
+#include <utility>
+#include <vector>
 
 #include "flash_bwd_fused_tc.cuh"
 #include "tma_host.cuh"
@@ -18,12 +20,15 @@ static bool fused_covered(const fa_flash_shape *s) {
          (s->D == 64 || s->D == 128) && s->dropout_p == 0.f;
 }
 
-// fp32 dq accumulator (B, H, Mpad, D), then 16 bytes that hold the kernel's work-item counter
+// Workspace: fp32 dq accumulator (B, H, Mpad, D) | 16 bytes that hold the kernel's work-item
+// counter.
 static int64_t fused_dq_acc_bytes(const fa_flash_shape *s) {
   const int64_t mpad = ((int64_t)s->M + 127) / 128 * 128;
   return (int64_t)s->B * s->H * mpad * s->D * 4;
 }
-static int64_t fused_workspace_bytes(const fa_flash_shape *s) { return fused_dq_acc_bytes(s) + 16; }
+static int64_t fused_workspace_bytes(const fa_flash_shape *s) {
+  return fused_dq_acc_bytes(s) + 16;
+}
 
 // one persistent CTA per SM
 static int sm_count() {
@@ -32,6 +37,51 @@ static int sm_count() {
       cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
     return 0;
   return n;
+}
+
+// diff[i] holds +1 / -1 where coverage of unit i starts / ends; returns the maximal runs of
+// uncovered units as row ranges (unit = `rows_per_unit` rows, clipped to `rows`).
+static std::vector<std::pair<int, int>> zero_runs(const std::vector<int> &diff, int units,
+                                                  int rows_per_unit, int rows) {
+  std::vector<std::pair<int, int>> runs;
+  int seen = 0, run_begin = -1;
+  for (int u = 0; u <= units; ++u) {
+    if (u < units) seen += diff[u];
+    const bool uncovered = u < units && seen == 0;
+    if (uncovered && run_begin < 0) run_begin = u;
+    if (!uncovered && run_begin >= 0) {
+      const int end = u * rows_per_unit < rows ? u * rows_per_unit : rows;
+      runs.emplace_back(run_begin * rows_per_unit, end);
+      run_begin = -1;
+    }
+  }
+  return runs;
+}
+
+// Row ranges [begin, end) of dk / dv whose key block no query tile sees (keys past the causal
+// triangle when N > M + ..., keys without a pair of the branch in a piecewise launch): the kernel
+// skips those blocks.
+static std::vector<std::pair<int, int>> unvisited_key_rows(const fa_flash_shape *s, int mode, int w) {
+  const int BM = 128, BN = 128;
+  const int p_seq = s->N - s->M, num_m_tiles = (s->M + BM - 1) / BM;
+  const int num_blocks = (s->N + BN - 1) / BN;
+  std::vector<int> diff(num_blocks + 1, 0);
+  for (int nb = 0; nb < num_blocks; ++nb) {
+    const int n0 = nb * BN;
+    int lo = 0, hi = num_m_tiles;
+    if (s->causal) lo = (n0 - p_seq > 0 ? n0 - p_seq : 0) / BM;
+    if (mode == 1) {
+      const int lim = w - p_seq + n0 + BN - 1;
+      const int cap = lim <= 0 ? 0 : (lim + BM - 1) / BM;
+      hi = cap < hi ? cap : hi;
+    } else if (mode == 2) {
+      const int lim = w - p_seq + n0 - (BM - 1);
+      const int flo = lim <= 0 ? 0 : (lim + BM - 1) / BM;
+      lo = flo > lo ? flo : lo;
+    }
+    if (lo < hi) ++diff[nb], --diff[nb + 1];
+  }
+  return zero_runs(diff, num_blocks, BN, s->N);
 }
 
 template <typename T, int D>
@@ -60,6 +110,7 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
   p.status = device_status_word();
   p.mode = mode, p.w = w, p.dv_accumulate = dv_accumulate;
   p.dk = dk->ptr, p.dv = dv->ptr, p.sdk = strides_of(dk), p.sdv = strides_of(dv);
+  p.dq = dq->ptr, p.sdq = strides_of(dq);
   fp.dq_acc = workspace;
   fp.Mpad = (s->M + 127) / 128 * 128;
   fp.sched = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(workspace) + fused_dq_acc_bytes(s));
@@ -76,6 +127,16 @@ static int launch_fused(const fa_flash_shape *s, const fa_tensor4 *q, const fa_t
     if (items > 0x7fffffff) return FA_ERR_TOO_LARGE;
     if (sms <= 0) return FA_ERR_LAUNCH;
     fp.num_items = (int)items;
+    // dk / dv rows of key blocks that walk no query tile (which the kernel skips) get their zeros
+    // here (dv not where it is added to)
+    for (const auto &r : unvisited_key_rows(s, mode, w)) {
+      if (r.first >= r.second) continue;
+      dim3 zgrid((r.second - r.first + 15) / 16, s->Hk, s->B);
+      zero_rows_kernel<T, D><<<zgrid, 256, 0, stream>>>(dk->ptr, strides_of(dk), r.first, r.second);
+      if (!dv_accumulate)
+        zero_rows_kernel<T, D><<<zgrid, 256, 0, stream>>>(dv->ptr, strides_of(dv), r.first, r.second);
+      FA_CHECK_LAUNCH();
+    }
     // persistent: a CTA takes item `blockIdx.x`, then items handed out by the counter
     dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
     kern<<<grid, kFusedThreads, C::kTotal, stream>>>(mq, mdo, mk, mv, mdk, mdv, fp);

@@ -66,10 +66,10 @@ enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB
 
 struct FusedBwdParams {
   BwdTcParams base;
-  float *dq_acc;   // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
-  int Mpad;        // M rounded up to a multiple of 128
-  unsigned *sched; // work-item counter, zeroed before the launch (see the kernel)
-  int num_items;   // key blocks x (batch, kv head) pairs
+  float *dq_acc;      // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
+  int Mpad;           // M rounded up to a multiple of 128
+  unsigned *sched;    // work-item counter; zero at launch and at exit (see the kernel)
+  int num_items;      // key blocks x (batch, kv head) pairs
 };
 
 // fp32 add of `bytes` contiguous bytes of shared memory into global memory, done by the copy
@@ -87,7 +87,7 @@ __device__ __forceinline__ void bulk_wait_read_1() {
   asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
 }
 // waits until every group has finished reading its shared-memory source (what a CTA owes before
-// it gives its shared memory back; the additions themselves complete by the end of the grid)
+// it gives its shared memory back)
 __device__ __forceinline__ void bulk_wait_read_all() {
   asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
 }
@@ -132,7 +132,8 @@ struct FusedItem {
 // PERSISTENT: the grid is one CTA per SM.  A CTA works through items (key block, pair) in the
 // order of grouped_cta(): its first item is its block index, every further one comes from a
 // global counter (`sched`, zero at launch), fetched one item ahead by the producer thread and
-// handed to the other warps through a four-slot ring in shared memory.  Barriers, TMEM and the
+// handed to the other warps through a four-slot ring in shared memory (items whose key block no
+// query sees are skipped by the producer: the launcher zero-fills their dk / dv rows).  Barriers, TMEM and the
 // operand rings are set up once per CTA and their phases simply keep counting across items, so
 // the tail of an item overlaps the head of the next: while the element-wise warps convert dV and
 // dK of item i (dV into the shared memory of V, dK into the P^T / dS^T tile, both dead by then)
@@ -164,22 +165,25 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   const int num_m_tiles = (p.M + BM - 1) / BM;
   const int total = fp.num_items;
 
+  // query tiles [mt_lo, mt_hi) that the key block starting at n0 walks
+  auto tile_range = [&](int n0, int &mt_lo, int &mt_hi) {
+    mt_lo = 0;
+    if (p.causal) mt_lo = max(0, n0 - p_seq) / BM;
+    mt_hi = num_m_tiles;
+    if (p.mode == 1) {  // query tiles that hold a near pair
+      const int lim = p.w - p_seq + n0 + BN - 1;
+      mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+    } else if (p.mode == 2) {  // query tiles that hold a far pair
+      const int lim = p.w - p_seq + n0 - (BM - 1);
+      mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
+    }
+  };
   auto decode = [&](int w) -> FusedItem {
     const CtaCoord cta = grouped_cta((unsigned)w, p.num_blocks, p.B * p.Hk, p.group_size);
     FusedItem it;
     it.n0 = cta.blk * BN, it.hk = cta.pair % p.Hk, it.b = cta.pair / p.Hk;
-    int mt_lo = 0;
-    if (p.causal) mt_lo = max(0, it.n0 - p_seq) / BM;
-    int mt_hi = num_m_tiles;
-    if (p.mode == 1) {  // query tiles that hold a near pair
-      const int lim = p.w - p_seq + it.n0 + BN - 1;
-      mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
-    } else if (p.mode == 2) {  // query tiles that hold a far pair
-      const int lim = p.w - p_seq + it.n0 - (BM - 1);
-      mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
-    }
-    it.mt_lo = mt_lo, it.mt_hi = mt_hi;
-    it.T_tiles = max(0, mt_hi - mt_lo) * G;
+    tile_range(it.n0, it.mt_lo, it.mt_hi);
+    it.T_tiles = max(0, it.mt_hi - it.mt_lo) * G;
     return it;
   };
   // the id of this CTA's `ic`-th item, as published by the producer thread (>= total: no more)
@@ -190,7 +194,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
 
-  const FusedItem first = decode(blockIdx.x);   // the grid never exceeds the number of items
+  // Next work item with at least one tile, starting at w: items past the end of the list (>= total)
+  // end the CTA.  Every id beyond the CTA's first comes from the global counter; whoever makes the
+  // last fetch of the launch (every CTA ends on exactly one fetch past the end, so there are `total`
+  // in all) puts the counter back to zero for the next launch.
+  auto next_real = [&](int w) -> int {
+    while (w < total && decode(w).T_tiles == 0) {
+      const unsigned fetched = atomicAdd(fp.sched, 1u);
+      if (fetched == (unsigned)total - 1u) atomicExch(fp.sched, 0u);
+      w = (int)gridDim.x + (int)fetched;
+    }
+    return w;
+  };
+  int w_first = 0;   // producer thread only
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar(FB_KV_FULL), 1);   // K
@@ -221,7 +237,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     mbar_init(bar(FB_PD_STORED), 1);
     for (int s = 0; s < 4; ++s) mbar_init(bar(FB_ITEM_FULL + s), 1);
     fence_barrier_init();
-    item_ring[0] = (int)blockIdx.x;
+    w_first = next_real((int)blockIdx.x);   // the grid never exceeds the number of items
+    item_ring[0] = w_first;
     mbar_arrive(bar(FB_ITEM_FULL + 0));
     // The loads of the first tile go out right here, before the TMEM allocation and the CTA-wide
     // barrier below, so that their latency (the first bytes of K, V, Q, dO come from HBM) runs
@@ -232,7 +249,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     tma_prefetch_desc(&map_do);
     tma_prefetch_desc(&map_dk);
     tma_prefetch_desc(&map_dv);
-    if (first.T_tiles > 0) {
+    if (w_first < total) {
+      const FusedItem first = decode(w_first);
       const int h0 = first.hk * G, m00 = first.mt_lo * BM;
       mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
@@ -264,6 +282,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       int sq = 0, phq = 1, sd = 0, phd = 1;   // ring slot and the "free" parity to wait for
       int inflight_q = 0, inflight_do = 0;    // loads requested (for the drain after an abort)
       int real = 0;                           // items with tiles handled so far
+      uint32_t gt = 0;                        // tiles of those items
       bool pending = false;                   // dV / dK of the previous such item not stored yet
       int pn0 = 0, phk = 0, pb = 0;           // its coordinates
       auto load_q = [&](const FusedItem &it, int h, int mt) {
@@ -300,14 +319,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         bulk_commit();
         return true;
       };
-      int w = blockIdx.x, ic = 0;
+      int w = w_first, ic = 0;
       while (w < total && ok) {
-        // fetch the id of the next item now, so that its latency hides behind this item
-        const int w_next = (int)gridDim.x + (int)atomicAdd(fp.sched, 1u);
-        item_ring[(ic + 1) & 3] = w_next;
-        mbar_arrive(bar(FB_ITEM_FULL + ((ic + 1) & 3)));
+        // ask for the id of the next item now; the answer is looked at after this item's first
+        // loads have gone out, so its latency hides behind them
+        const unsigned fetched = atomicAdd(fp.sched, 1u);
+        int w_next = total;
         const FusedItem it = decode(w);
-        if (it.T_tiles > 0) {
+        {
           int h = it.hk * G, mt = it.mt_lo;
           const bool preissued = (ic == 0);   // tile 0, K and V of the first item: see set-up
           if (preissued) {
@@ -321,8 +340,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             load_do(it, h, mt);
             if (pending) {
               ok = store_dv();
-              // K is free once every product of the previous item has completed
-              if (ok) ok = mbar_wait(bar(FB_DONE), (real - 1) & 1, actx, 723);
+              // K is free once the last product that reads it, dQ of the previous item's last
+              // tile, has completed
+              if (ok) ok = mbar_wait(bar(FB_DQ_FULL), (gt - 1) & 1, actx, 723);
               if (!ok) break;
             }
             mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
@@ -343,6 +363,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           }
           pending = true, pn0 = it.n0, phk = it.hk, pb = it.b;
           ++real;
+          // hand the next item's id to the other warps
+          if (fetched == (unsigned)total - 1u) atomicExch(fp.sched, 0u);
+          w_next = next_real((int)gridDim.x + (int)fetched);
+          item_ring[(ic + 1) & 3] = w_next;
+          mbar_arrive(bar(FB_ITEM_FULL + ((ic + 1) & 3)));
           if (++sq == NQ) sq = 0, phq ^= 1;
           if (++sd == NDO) sd = 0, phd ^= 1;
           if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
@@ -357,14 +382,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             if (++sd == NDO) sd = 0, phd ^= 1;
             if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
           }
-        } else if (pending) {
-          // an item without tiles: nothing to load, so the previous item's stores go out now
-          ok = store_dv();
-          if (ok) ok = store_dk();
           if (!ok) break;
-          bulk_wait_read_all();
-          mbar_arrive(bar(FB_PD_STORED));
-          pending = false;
+          gt += (uint32_t)it.T_tiles;
+          // K and V of the next item are read by nobody else: start them towards L2 now, a couple
+          // of tiles before this item ends (any earlier and they would be evicted again)
+          if (w_next < total) {
+            const FusedItem nx = decode(w_next);
+            for (int s = 0; s < KSUB; ++s) {
+              tma_prefetch_l2_4d(&map_k, s * 64, nx.n0, nx.hk, nx.b);
+              tma_prefetch_l2_4d(&map_v, s * 64, nx.n0, nx.hk, nx.b);
+            }
+          }
         }
         w = w_next, ++ic;
       }
@@ -422,7 +450,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         const int w = ring_item(ic, 801);
         if (w < 0 || w >= total) break;
         const FusedItem it = decode(w);
-        if (it.T_tiles == 0) continue;
         ok = mbar_wait(bar(FB_KV_FULL), real & 1, actx, 811);
         // the score columns still hold dP^T of the previous item's last tile until the
         // element-wise warps have it in registers
@@ -569,7 +596,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     for (int ic = 0; ok; ++ic) {
       // every wait is bounded, so all four warps reach each vote; they leave together or not at all
       const int w = ring_item(ic, 920);
-      if (!red_warps_all(w >= 0)) break;
+      if (!red_warps_all(w >= 0)) {
+        ok = false;
+        break;
+      }
       if (w >= total) break;
       const FusedItem it = decode(w);
       int h = it.hk * G, mt = it.mt_lo;
@@ -683,15 +713,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           *reinterpret_cast<uint4 *>(orow + j * 8) = pack8(ov + 8 * j, scale);
         }
       };
-      if (it.T_tiles == 0) {
-        // no query sees these keys: their gradients are zero (dV untouched where it is added to)
-        uint32_t ov[QC];
-#pragma unroll
-        for (int i = 0; i < QC; ++i) ov[i] = 0u;
-        direct(p.dk, p.sdk, ov, 1.f, false);
-        if (!p.dv_accumulate) direct(p.dv, p.sdv, ov, 1.f, false);
-        continue;
-      }
       int mt = it.mt_lo;   // query tile of the current tile
 
       for (int t = 0; t < it.T_tiles; ++t, ++gt) {
@@ -893,6 +914,19 @@ __global__ void __launch_bounds__(256)
     *reinterpret_cast<uint4 *>(orow + g * 16) = v[0];
     *reinterpret_cast<uint4 *>(orow + g * 16 + 8) = v[1];
   }
+}
+
+// Zero-fill of rows [r_begin, r_end) of every (batch, head) of dk / dv: the keys no query sees
+// (past the causal triangle, or without a pair of the branch in a piecewise launch), whose blocks
+// the kernel above skips.
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+    zero_rows_kernel(void *out, Strides so, int r_begin, int r_end) {
+  const int m = r_begin + blockIdx.x * 16 + (threadIdx.x >> 4);
+  if (m >= r_end) return;
+  T *orow = row_ptr_mut<T>(out, so, blockIdx.z, blockIdx.y, m);
+  for (int c = (threadIdx.x & 15) * 8; c < D; c += 128)
+    *reinterpret_cast<uint4 *>(orow + c) = make_uint4(0u, 0u, 0u, 0u);
 }
 
 }  // namespace tc

@@ -130,8 +130,9 @@ int fa_flash_bwd_dq(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tenso
 /* dk, dv (Hk heads) and dq from ONE pass over the score tiles (head_dim 64 / 128 on the
  * tensor-core path): S and dP are computed once instead of once per kernel.  Replaces the pair
  * of launches `_bwd_kv_kernel` + `_bwd_q_kernel` (src/flag_attn/flash.py:204-249).  dq is
- * accumulated with fp32 global reductions in `workspace`, so it is reproducible to fp32
- * rounding only (dk, dv are bitwise reproducible).  A caller that needs bitwise reproducible
+ * accumulated with fp32 global reductions in `workspace` (which also holds the 16 bytes of the
+ * persistent kernel's work-item counter), so it is reproducible to fp32 rounding only (dk, dv
+ * are bitwise reproducible).  A caller that needs bitwise reproducible
  * gradients (the `_bwd_q_kernel` contract: "no atomics") calls fa_flash_bwd_dkdv + fa_flash_bwd_dq
  * instead: which of the two a process uses is the caller's choice of entry point, nothing else
  * (the Python host chooses by torch.are_deterministic_algorithms_enabled() or

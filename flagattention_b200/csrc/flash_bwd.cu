@@ -87,6 +87,8 @@ struct TotalLaunch {
 };
 
 namespace tc {
+int total_attention_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
+                       const float *lse, float *total, cudaStream_t stream);
 int flash_bwd_dq_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,
                     const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,
                     const float *delta, const fa_tensor4 *dq, cudaStream_t stream);
@@ -167,6 +169,9 @@ extern "C" int fa_total_attention(const fa_flash_shape *s, const fa_tensor4 *q,
   if (int st = validate_shape(s)) return st;
   if (int st = validate_tensors({q, k})) return st;
   if (!lse || !total) return FA_ERR_BAD_ARG;
+  // head_dim 64 / 128 run on tcgen05; everything else on the shape-generic kernel
+  const int tc_status = tc::total_attention_tc(s, q, k, lse, total, static_cast<cudaStream_t>(stream));
+  if (tc_status <= 0) return tc_status;
   return dispatch_dtype_d(s->dtype, s->D,
                           TotalLaunch{s, q, k, lse, total, static_cast<cudaStream_t>(stream)});
 }

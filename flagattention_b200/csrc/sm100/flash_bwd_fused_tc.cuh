@@ -15,17 +15,21 @@
 //   warps 18..21 dQ reduction: TMEM -> shared-memory staging -> cp.reduce.async.bulk
 //   warp 22      stages lse / delta of every tile in shared memory
 //
-// TMEM (512 columns):  S^T, then dP^T | dQ | dK | dV.
+// TMEM (512 columns):  S^T, then dP^T (128) | dQ (D), P^T over its first 64 columns | dK | dV.
 //   The two score products of a tile share one 128-column region: dP^T is issued as soon as the
 //   element-wise warps hold S^T in registers, S^T of the next tile as soon as they hold dP^T.
-//   dQ has columns of its own, so its slow read-out never holds a GEMM back.
+//   P^T goes back to TMEM as packed 16-bit pairs and is the TMEM A operand of dV += P^T dO: no
+//   shared-memory store, no async-proxy fence, and P^T never competes with dS^T for a buffer.
+//   At head_dim 128 all 512 columns are taken, so P^T(t+1) borrows the first 64 columns of dQ:
+//   they are free between the read-out of dQ(t)'s first two quarters and the issue of dQ(t+1)
+//   (head_dim 64 has columns to spare and keeps P^T apart).
 // Shared memory:       K, V resident | Q ring | dO ring | one 16-bit 128 x 128 tile "PD" | dQ staging.
-//   PD holds P^T (A operand of dV += P^T dO), then dS^T of the same tile: the K-major A operand of
-//   dK += dS^T Q and, under a second descriptor, the MN-major A operand of dQ = dS K.
+//   PD holds dS^T of a tile: the K-major A operand of dK += dS^T Q and, under a second descriptor,
+//   the MN-major A operand of dQ = dS K.
 //
-// Issue order of a tile (tensor pipe, in order):   dP^T(t) | dV(t) | S^T(t+1) | dQ(t) | dK(t)
-// Element-wise order:                              phase 1 (t) | phase 2 (t)
-//   phase 1: P^T = exp2(S^T * scale - L) -> PD       phase 2: dS^T = P^T * (dP^T - delta) -> PD
+// Issue order (tensor pipe):  dP^T(t) | dV(t) | S^T(t+1) | dQ(t) | dK(t)
+// Element-wise order:         phase 1 (t) | phase 2 (t)
+//   phase 1: P^T = exp2(S^T * scale - L) -> TMEM     phase 2: dS^T = P^T * (dP^T - delta) -> PD
 #pragma once
 
 #include "flash_bwd_tc.cuh"
@@ -52,7 +56,10 @@ struct FusedBwdCfg {
   static constexpr int kStats = kMisc + 32;            // -lse*log2e [128] | -delta [128] of a tile
   static constexpr int kTotal = kStats + 2 * 128 * 4 + 1024;
   static constexpr int kTmemCols = 512;
-  static constexpr int kColA = 0, kColQ = 128, kColDK = 256, kColDV = 256 + D;
+  static constexpr int NH = 1;                         // parts dQ of a tile is produced in
+  // head_dim 128: dQ at 128..255 with P^T over 128..191; head_dim 64: P^T at 128..191, dQ at 192..255
+  static constexpr bool kPAliasesDQ = (D == 128);
+  static constexpr int kColA = 0, kColP = 128, kColQ = (D == 128 ? 128 : 192), kColDK = 256, kColDV = 256 + D;
   static_assert(kPdBytes >= kTile, "dK is staged in the P^T / dS^T tile");
   static_assert(kTotal <= 232448, "shared memory budget");
 };
@@ -62,7 +69,7 @@ enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB
                 FB_PT_FULL = 13, FB_PT_FREE = 14, FB_DS_FULL = 15, FB_DS_FREE = 16,
                 FB_DQ_FULL = 17, FB_DQ_FREE = 18, FB_DONE = 19, FB_LSE_FULL = 20, FB_DLT_FULL = 21,
                 FB_V_FULL = 22, FB_DV_STAGED = 23, FB_DK_STAGED = 24, FB_PD_STORED = 25,
-                FB_ITEM_FULL = 26 /* .. 29 */ };
+                FB_ITEM_FULL = 26 /* .. 29 */, FB_DQ_HALF = 30 };
 
 struct FusedBwdParams {
   BwdTcParams base;
@@ -229,6 +236,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     mbar_init(bar(FB_DS_FREE), 1);
     mbar_init(bar(FB_DQ_FULL), 1);
     mbar_init(bar(FB_DQ_FREE), 4);
+    mbar_init(bar(FB_DQ_HALF), 4);
     mbar_init(bar(FB_DONE), 1);
     mbar_init(bar(FB_LSE_FULL), 1);
     mbar_init(bar(FB_DLT_FULL), 1);
@@ -340,9 +348,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             load_do(it, h, mt);
             if (pending) {
               ok = store_dv();
-              // K is free once the last product that reads it, dQ of the previous item's last
-              // tile, has completed
-              if (ok) ok = mbar_wait(bar(FB_DQ_FULL), (gt - 1) & 1, actx, 723);
+              // K is free once every product of the previous item has completed (the last one
+              // issued reads it).  This thread does not follow the per-tile barriers phase by
+              // phase, so it waits on the per-item one.
+              if (ok) ok = mbar_wait(bar(FB_DONE), (real - 1) & 1, actx, 723);
               if (!ok) break;
             }
             mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
@@ -419,7 +428,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     if (lane == 0) {
       constexpr uint32_t idesc_s = instr_desc_f16(BN, BM, TcElem<T>::kFormat, 0, 0);   // S^T, dP^T
       constexpr uint32_t idesc_acc = instr_desc_f16(BN, D, TcElem<T>::kFormat, 0, 1);  // dV, dK
-      constexpr uint32_t idesc_dq = instr_desc_f16(BM, D, TcElem<T>::kFormat, 1, 1);   // dQ
+      constexpr uint32_t idesc_dq = instr_desc_f16(BM, D / C::NH, TcElem<T>::kFormat, 1, 1);  // dQ
       constexpr uint32_t kTile16 = C::kTile >> 4;
       const uint32_t k_lo = smem_desc_lo(smem + C::kK, 0), v_lo = smem_desc_lo(smem + C::kV, 0);
       const uint32_t k_mn_lo = smem_desc_lo(smem + C::kK, BN * 128);     // K as MN-major B of dQ
@@ -446,6 +455,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       int sq = 0, phq = 0, sd = 0, phd = 0;
       int real = 0;            // items with tiles so far
       uint32_t gt = 0;         // tiles so far, over all items: the phase of every per-tile barrier
+      uint32_t gh = 0;         // dQ parts so far: the phase of DQ_FULL / DQ_FREE
+      // part `hf` of dQ = dS K into the dQ columns, a fresh accumulator: the read-out of the part
+      // before must be over
+      auto issue_dq_part = [&](int hf) -> bool {
+        if (gh > 0 && !mbar_wait(bar(FB_DQ_FREE), (gh - 1) & 1, actx, 818)) return false;
+        tc_fence_after();
+        const uint32_t b_lo = k_mn_lo + hf * ((BN * 128) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t off16 = (kk * 16 * 128) >> 4;
+          mma_ss_lo(tmem + C::kColQ, pd_mn_lo + off16, b_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(FB_DQ_FULL));
+        ++gh;
+        return true;
+      };
       for (int ic = 0; ok; ++ic) {
         const int w = ring_item(ic, 801);
         if (w < 0 || w >= total) break;
@@ -478,18 +503,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             }
             mma_commit(bar(FB_DP_FULL));
           }
-          // dV += P^T(t) dO(t), P^T from shared memory
+          // the second part of dQ of the tile before (head_dim 128): its first part has been read
+          // out meanwhile; PD is free once it is through
+          if (C::NH == 2 && t > 0) {
+            ok = issue_dq_part(1);
+            if (!ok) break;
+            mma_commit(bar(FB_DS_FREE));
+          }
+          // dV += P^T(t) dO(t), P^T from TMEM
           ok = mbar_wait(bar(FB_PT_FULL), par, actx, 815);
           if (!ok) break;
           tc_fence_after();
           {
             const uint32_t b_lo = do_mn_lo + sd * kTile16;
 #pragma unroll
-            for (int kk = 0; kk < BM / 16; ++kk) {
-              const uint32_t a_off16 = ((kk / 4) * 128 * 128 + (kk % 4) * 32) >> 4;
-              mma_ss_lo(tmem + C::kColDV, pd_k_lo + a_off16, b_lo + ((kk * 16 * 128) >> 4), idesc_acc,
-                        kk > 0 ? 1u : acc);
-            }
+            for (int kk = 0; kk < BM / 16; ++kk)
+              mma_ts_lo(tmem + C::kColDV, tmem + C::kColP + kk * 8, b_lo + ((kk * 16 * 128) >> 4),
+                        idesc_acc, kk > 0 ? 1u : acc);
             mma_commit(bar(FB_DO_FREE + sd));
             mma_commit(bar(FB_PT_FREE));
           }
@@ -501,17 +531,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             ok = issue_s(nsq, nphq);
             if (!ok) break;
           }
-          // dQ(t) = dS(t) K, a fresh accumulator: the read-out of the previous dQ must be over
+          // the first part of dQ(t) = dS(t) K
           ok = mbar_wait(bar(FB_DS_FULL), par, actx, 817);
-          if (ok && gt > 0) ok = mbar_wait(bar(FB_DQ_FREE), (gt - 1) & 1, actx, 818);
+          if (ok) ok = issue_dq_part(0);
           if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            const uint32_t off16 = (kk * 16 * 128) >> 4;
-            mma_ss_lo(tmem + C::kColQ, pd_mn_lo + off16, k_mn_lo + off16, idesc_dq, kk > 0 ? 1u : 0u);
-          }
-          mma_commit(bar(FB_DQ_FULL));
           // dK += dS^T(t) Q(t)
           {
             const uint32_t b_lo = q_mn_lo + sq * kTile16;
@@ -522,12 +545,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                         kk > 0 ? 1u : acc);
             }
             mma_commit(bar(FB_Q_FREE + sq));
-            mma_commit(bar(FB_DS_FREE));
+            if (C::NH == 1) mma_commit(bar(FB_DS_FREE));
           }
           sq = nsq, phq = nphq;
           if (++sd == NDO) sd = 0, phd ^= 1;
         }
         if (!ok) break;
+        if (C::NH == 2) {   // the second part of dQ of the item's last tile
+          ok = issue_dq_part(1);
+          if (!ok) break;
+          mma_commit(bar(FB_DS_FREE));
+        }
         mma_commit(bar(FB_DONE));
         ++real;
       }
@@ -592,7 +620,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     constexpr int QC = D / 4;                 // columns per quarter
     int buf = 0;
     bool ok = true;
-    uint32_t gt = 0;
+    uint32_t gt = 0, gh = 0;
+    constexpr int QPH = 4 / C::NH;            // quarters per part of dQ
     for (int ic = 0; ok; ++ic) {
       // every wait is bounded, so all four warps reach each vote; they leave together or not at all
       const int w = ring_item(ic, 920);
@@ -607,16 +636,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         // the tile's block of the workspace: D / 4 runs of (128 queries x 4 columns), contiguous
         float *dst = fp.dq_acc + (((int64_t)it.b * p.H + h) * (fp.Mpad / BM) + mt) * (int64_t)(BM * D);
         if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
-        ok = red_warps_all(mbar_wait(bar(FB_DQ_FULL), gt & 1, actx, 921));
-        if (!ok) break;
-        tc_fence_after();
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd) {
+          if (qd % QPH == 0) {   // the next part of dQ
+            ok = red_warps_all(mbar_wait(bar(FB_DQ_FULL), gh & 1, actx, 921));
+            if (!ok) break;
+            ++gh;
+            tc_fence_after();
+          }
           uint32_t qr[QC];
-          if (QC == 32) tmem_ld32(tlane + C::kColQ + qd * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
-          else tmem_ld16(tlane + C::kColQ + qd * QC, qr);
+          if (QC == 32) tmem_ld32(tlane + C::kColQ + (qd % QPH) * QC, *reinterpret_cast<uint32_t(*)[32]>(qr));
+          else tmem_ld16(tlane + C::kColQ + (qd % QPH) * QC, qr);
           tmem_wait_ld();
-          if (qd == 3) {
+          if (C::kPAliasesDQ && qd == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(FB_DQ_HALF));   // the next P^T may take the first 64 columns
+          }
+          if (qd % QPH == QPH - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(FB_DQ_FREE));   // the next dQ may overwrite the columns
@@ -639,6 +676,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           }
           buf ^= 1;
         }
+        if (!ok) break;
       }
     }
     if (issuer) bulk_wait_read_all();   // shared memory must outlive the copy engine's reads
@@ -719,7 +757,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         const int m0 = mt * BM;
         if (++mt == it.mt_hi) mt = it.mt_lo;
 
-        // ---- phase 1: P^T = exp2(S^T * scale - lse) -> PD ----
+        // ---- phase 1: P^T = exp2(S^T * scale - lse) -> TMEM ----
         ok = mbar_wait(bar(FB_LSE_FULL), gt & 1, actx, 910);
         if (ok) ok = mbar_wait(bar(FB_S_FULL), gt & 1, actx, 911);
         ok = __all_sync(0xffffffffu, ok);
@@ -775,17 +813,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             pv[c + 1] = ex2(pv[c + 1]);
             pk[c >> 1] = TcElem<T>::pack(pv[c], pv[c + 1]);
           }
-          // PD still holds dS^T of the tile before until its dQ and dK products have read it, and,
-          // at the first tile of an item, the staged dK of the item before until it is stored
-          if (gt > 0) ok = mbar_wait(bar(FB_DS_FREE), (gt - 1) & 1, actx, 912);
-          if (ok && t == 0 && real > 0) ok = mbar_wait(bar(FB_PD_STORED), (real - 1) & 1, actx, 917);
+          // the P^T columns still hold P^T of the tile before until its dV product has read them
+          if (gt > 0) ok = mbar_wait(bar(FB_PT_FREE), (gt - 1) & 1, actx, 912);
+          // ... and, where P^T borrows columns of dQ, dQ of the tile before until they are read out
+          if (C::kPAliasesDQ && ok && gt > 0) ok = mbar_wait(bar(FB_DQ_HALF), (gt - 1) & 1, actx, 918);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          store_pd(pk);
+          tmem_st16(tlane + C::kColP + cg * 16, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
         }
         // ---- phase 2: dS^T = P^T * (dP^T - delta) -> PD ----
-        // Its operands are there by now (dP^T(t) was issued as soon as S^T(t) had been read), so the
-        // first TMEM load goes out before the proxy fence of phase 1 and hides behind it.
+        // Its operands are there by now (dP^T(t) was issued as soon as S^T(t) had been read).
         ok = mbar_wait(bar(FB_DLT_FULL), gt & 1, actx, 909);
         if (ok) ok = mbar_wait(bar(FB_DP_FULL), gt & 1, actx, 913);
         ok = __all_sync(0xffffffffu, ok);
@@ -793,9 +834,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         tc_fence_after();
         uint32_t sr0[16];
         tmem_ld16(tlane + C::kColA + cg * 32, sr0);
-        fence_proxy_async_smem();   // the MMA reads PD through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(FB_PT_FULL));
         {
           uint32_t pk[16];
           // P * (dP - delta) of 16 columns, two elements per instruction
@@ -828,8 +866,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             if (lane == 0) mbar_arrive(bar(FB_DP_LOADED));   // the next S^T may overwrite dP^T(t)
             half_ds(1, sr1);
           }
-          // PD still holds P^T(t) until dV(t) has read it
-          ok = mbar_wait(bar(FB_PT_FREE), gt & 1, actx, 914);
+          // PD still holds dS^T of the tile before until its dQ and dK products have read it, and,
+          // at the first tile of an item, the staged dK of the item before until it is stored
+          if (gt > 0) ok = mbar_wait(bar(FB_DS_FREE), (gt - 1) & 1, actx, 914);
+          if (ok && t == 0 && real > 0) ok = mbar_wait(bar(FB_PD_STORED), (real - 1) & 1, actx, 917);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           store_pd(pk);
@@ -841,14 +881,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       if (!ok) break;
 
       // ---- write-out of dV and dK of this item ----
-      // dV is final once its last product has been committed (the PT_FREE wait that ended the loop),
-      // so it is converted and staged while dQ and dK of the last tile still run on the tensor
+      // dV is final once its last product has been committed, so it is converted and staged while dQ and dK of the last tile still run on the tensor
       // cores; dK follows after the last commit.  dV is staged in the shared memory of V and dK in
       // the P^T / dS^T tile (both dead by then) in the layout of an operand load, and the producer
       // thread sends them off as bulk tensor stores, which also drop the rows past N.  A dV that is
       // added to (the second launch of a piecewise backward) keeps per-thread global stores.
       {
         uint32_t ov[QC];
+        ok = mbar_wait(bar(FB_PT_FREE), (gt - 1) & 1, actx, 915);   // the last dV product
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         tc_fence_after();
         load_cols(C::kColDV, ov);
         if (!p.dv_accumulate) {

@@ -56,6 +56,7 @@ class PagedArgs(ctypes.Structure):
         ("bt_stride_s", ctypes.c_int64),
         ("out", ctypes.c_void_p), ("o_stride_s", ctypes.c_int64), ("o_stride_h", ctypes.c_int64),
         ("part_out", ctypes.c_void_p), ("part_max", ctypes.c_void_p), ("part_sum", ctypes.c_void_p),
+        ("causal_rows", ctypes.c_int32),
     ]
 
 

@@ -56,6 +56,17 @@ __global__ void __launch_bounds__(PagedCfg<D>::kWarps * 32) paged_decode_kernel(
   const int t_end = a.partition_size > 0 ? min(ctx, t_begin + a.partition_size) : ctx;
   const int BS = a.block_size;
   const bool group_in_block = (BS % 16 == 0) && (t_begin % 16 == 0);
+  // Several queries per head (a.causal_rows = Mq > 0): query head index = head * Mq + m, and query
+  // m of a head is the (Mq - 1 - m)-th from the end of the sequence, so it sees the tokens below
+  // ctx - (Mq - 1 - m).  This thread's two accumulator rows are g and g + 8 of the tile.
+  int row_end[2] = {t_end, t_end};
+  if (a.causal_rows > 0) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int m = (qt * 16 + g + 8 * r) % a.causal_rows;
+      row_end[r] = min(t_end, ctx - (a.causal_rows - 1 - m));
+    }
+  }
 
   // ---- query group -> shared (rows >= `rows` are zero) ---------------------
   {
@@ -172,13 +183,13 @@ __global__ void __launch_bounds__(PagedCfg<D>::kWarps * 32) paged_decode_kernel(
         Elem<T>::mma(s[1], qa, bb[2], bb[3]);
       }
     }
-    const bool tail = tok0 + 16 > t_end;
+    const bool tail = tok0 + 16 > min(row_end[0], row_end[1]);
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int tok = tok0 + j * 8 + 2 * t4 + (e & 1);
-        s[j][e] = (tail && tok >= t_end) ? -INFINITY : s[j][e] * qk_scale;
+        s[j][e] = (tail && tok >= row_end[e >> 1]) ? -INFINITY : s[j][e] * qk_scale;
       }
     // Running maximum with lazy rescaling: the accumulators are only rescaled when some row's
     // maximum grew by more than 2^8 (scores are already in the base-2 domain); otherwise the
@@ -189,13 +200,13 @@ __global__ void __launch_bounds__(PagedCfg<D>::kWarps * 32) paged_decode_kernel(
     for (int r = 0; r < 2; ++r) {
       float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
       mx = quad_max(mx);
-      m_new[r] = fmaxf(m_i[r], mx);  // finite: every group holds >= 1 valid token
+      m_new[r] = fmaxf(m_i[r], mx);  // -inf only while a row has not seen a token it may see
       need = need || (m_new[r] - m_i[r] > 8.f);
     }
     if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const float alpha = fast_exp2(m_i[r] - m_new[r]);
+        const float alpha = (m_new[r] == -INFINITY) ? 1.f : fast_exp2(m_i[r] - m_new[r]);
         l_i[r] *= alpha;
         m_i[r] = m_new[r];
 #pragma unroll
@@ -208,10 +219,11 @@ __global__ void __launch_bounds__(PagedCfg<D>::kWarps * 32) paged_decode_kernel(
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       float rs = 0.f;
+      const float m_ref = (m_i[r] == -INFINITY) ? 0.f : m_i[r];   // all scores -inf: P = 0
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        s[j][2 * r] = fast_exp2(s[j][2 * r] - m_i[r]);
-        s[j][2 * r + 1] = fast_exp2(s[j][2 * r + 1] - m_i[r]);
+        s[j][2 * r] = fast_exp2(s[j][2 * r] - m_ref);
+        s[j][2 * r + 1] = fast_exp2(s[j][2 * r + 1] - m_ref);
         rs += s[j][2 * r] + s[j][2 * r + 1];
       }
       l_i[r] += rs;
@@ -358,6 +370,8 @@ static int validate_paged(const fa_paged_args *a, bool need_ws) {
     return FA_ERR_BAD_ARG;
   if (a->num_q_heads % a->num_kv_heads != 0) return FA_ERR_BAD_ARG;
   if (a->partition_size % 16 != 0) return FA_ERR_BAD_ARG;
+  if (a->causal_rows < 0 || (a->causal_rows > 0 && (a->num_q_heads / a->num_kv_heads) % a->causal_rows != 0))
+    return FA_ERR_BAD_ARG;
   const int D = a->head_size;
   if (!(D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) return FA_ERR_UNSUPPORTED;
   if (!aligned16(a->query) || !aligned16(a->key_cache) || !aligned16(a->value_cache) ||

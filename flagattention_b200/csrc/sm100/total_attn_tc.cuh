@@ -11,7 +11,7 @@
 //   warp 18      stages -lse * log2(e) of every tile in shared memory (broadcast reads)
 // At the end the four column groups of a key row are added through shared memory and the 128
 // sums are written.  One exponential per score bounds the kernel (the ex2 unit, not the tensor
-// pipe); two CTAs share an SM (256 TMEM columns, 96 KB of shared memory each at head_dim 128).
+// pipe).
 #pragma once
 
 #include "../attn_params.cuh"
@@ -50,7 +50,7 @@ enum TotalBar { TB_K_FULL = 0, TB_Q_FULL = 1, TB_Q_FREE = 3, TB_S_FULL = 5, TB_S
                 TB_LSE_FULL = 9, TB_LSE_FREE = 11 };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(TotalTcCfg<D>::kThreads, 2)
+__global__ void __launch_bounds__(TotalTcCfg<D>::kThreads, 1)
     total_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                               const __grid_constant__ CUtensorMap map_k, const TotalTcParams p) {
   using C = TotalTcCfg<D>;

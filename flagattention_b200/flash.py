@@ -110,13 +110,19 @@ def _identity_block_table(B, blocks_per_batch, id_stride, device):
     return tab
 
 
-def _decode_covered(q, k, v):
-    """Single-query forward (M == 1) that the paged-decode kernels can run directly on k and v:
-    the keys of a batch element are then a block table of 16-token blocks in place."""
+_DECODE_MAX_ROWS = 64   # query rows (group x queries) per kv head the gather kernel is given
+
+
+def _decode_covered(q, k, v, causal=False):
+    """Decode-shaped forward (a few queries per head, at most _DECODE_MAX_ROWS rows per kv head)
+    that the paged-decode kernels can run directly on k and v: the keys of a batch element are then
+    a block table of 16-token blocks in place."""
     B, H, M, D = q.shape
-    N = k.shape[2]
-    if M != 1 or N % 16 != 0 or N == 0:
+    N, Hk = k.shape[2], k.shape[1]
+    if M < 1 or N % 16 != 0 or N == 0 or (H // Hk) * M > _DECODE_MAX_ROWS:
         return False
+    if causal and M > 1 and N < M:
+        return False      # rows that see no key at all: the tile kernels give them their zeros
     if k.stride() != v.stride() or k.stride(3) != 1 or k.data_ptr() % 16 or v.data_ptr() % 16:
         return False
     sb, sh, sl, _ = k.stride()
@@ -125,10 +131,11 @@ def _decode_covered(q, k, v):
     return True
 
 
-def _decode_forward(q, k, v, sm_scale):
-    """o for M == 1 through fa_paged_decode / fa_paged_reduce (an HBM-bound gather kernel that
-    streams K and V once), instead of the split-KV tile kernels."""
-    B, H, _, D = q.shape
+def _decode_forward(q, k, v, sm_scale, causal=False):
+    """o for a few queries per head through fa_paged_decode / fa_paged_reduce (an HBM-bound gather
+    kernel that streams K and V once per 16 query rows of a kv head), instead of the split-KV tile
+    kernels.  The M queries of a head go in as M consecutive "query heads" of its kv head."""
+    B, H, M, D = q.shape
     Hk, N = k.shape[1], k.shape[2]
     BS = 16
     sb, sh, sl, _ = k.stride()
@@ -142,13 +149,14 @@ def _decode_forward(q, k, v, sm_scale):
     if N <= partition_size:
         partition_size = 0   # one pass, no reduction kernel
     table, ctx_lens = _identity_block_table(B, N // BS, sb // (BS * sl), q.device)
-    q2 = q.reshape(B, H, D)
+    q2 = q.reshape(B, H * M, D)
     if q2.stride(-1) != 1 or q2.data_ptr() % 16 or q2.stride(0) % 8 or q2.stride(1) % 8:
         q2 = q2.contiguous()
-    o = torch.empty((B, H, 1, D), dtype=q.dtype, device=q.device)
+    o = torch.empty((B, H, M, D), dtype=q.dtype, device=q.device)
     args = _C.PagedArgs()
     args.dtype = _C.dtype_code(q.dtype)
-    args.num_seqs, args.num_q_heads, args.num_kv_heads = B, H, Hk
+    args.num_seqs, args.num_q_heads, args.num_kv_heads = B, H * M, Hk
+    args.causal_rows = M if (causal and M > 1) else 0
     args.head_size, args.block_size = D, BS
     args.max_context_len = N
     args.block_table_is_i64 = 0
@@ -159,12 +167,12 @@ def _decode_forward(q, k, v, sm_scale):
     args.kv_stride_b, args.kv_stride_h, args.kv_stride_t = BS * sl, sh if Hk > 1 else 0, sl
     args.context_lens = ctx_lens.data_ptr()
     args.block_tables, args.bt_stride_s = table.data_ptr(), table.stride(0)
-    args.out, args.o_stride_s, args.o_stride_h = o.data_ptr(), H * D, D
+    args.out, args.o_stride_s, args.o_stride_h = o.data_ptr(), H * M * D, D
     stream = _C.stream_ptr(q.device)
     if partition_size:
         P = (N + partition_size - 1) // partition_size
-        part_out = torch.empty((B, H, P, D), dtype=torch.float32, device=q.device)
-        part_max = torch.empty((B, H, P), dtype=torch.float32, device=q.device)
+        part_out = torch.empty((B, H * M, P, D), dtype=torch.float32, device=q.device)
+        part_max = torch.empty((B, H * M, P), dtype=torch.float32, device=q.device)
         part_sum = torch.empty_like(part_max)
         args.part_out, args.part_max, args.part_sum = (part_out.data_ptr(), part_max.data_ptr(),
                                                        part_sum.data_ptr())
@@ -270,11 +278,20 @@ class FlashAttention(torch.autograd.Function):
         q, k, v = _C.kernel_ready(q), _C.kernel_ready(k), _C.kernel_ready(v)
 
         has_extra_return = True in (return_log_normalizer, return_total_attention, return_seed_offset)
-        if (M == 1 and dropout_p == 0 and not has_extra_return and not any(ctx.needs_input_grad[:3])
-                and _decode_covered(q, k, v)):
-            # decode step without gradients: nothing but o is needed, K and V are streamed once
+        if (M <= 16 and dropout_p == 0 and not has_extra_return and not any(ctx.needs_input_grad[:3])
+                and _decode_covered(q, k, v, causal)):
+            # decode step without gradients: nothing but o is needed.  One query always goes to the
+            # gather kernel, which streams K and V once; a few queries go there when the reference
+            # would split the keys (src/flag_attn/flash.py:59-61), i.e. when the tile grid alone
+            # would leave most of the GPU idle.
             with torch.cuda.device(q.device):
-                return _decode_forward(q, k, v, sm_scale)
+                take = M == 1
+                if not take:
+                    num_sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+                    cfg = get_fwd_config_kv_split(B, H, M, N, D, causal)
+                    take = num_splits_herustic(B, H, M, N, cfg[0], cfg[1], num_sms, 128) > 1
+                if take:
+                    return _decode_forward(q, k, v, sm_scale, causal)
 
         with torch.cuda.device(q.device):
             # dropout: one Philox counter per element of the (B, H, M, N) attention matrix

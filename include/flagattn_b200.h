@@ -232,6 +232,14 @@ typedef struct fa_paged_args {
   float *part_out;               /* [num_seqs, num_q_heads, P, head_size] fp32     */
   float *part_max;               /* [num_seqs, num_q_heads, P] fp32, base-2 domain */
   float *part_sum;               /* [num_seqs, num_q_heads, P] fp32                */
+  /* Several query tokens per head (0 = one, the decode case of the reference).  With
+   * causal_rows = Mq > 0 the query-head axis holds Mq consecutive queries of each head (index =
+   * head * Mq + m; num_q_heads counts them all, and num_q_heads / num_kv_heads is a multiple of
+   * Mq); they are the LAST Mq tokens of the sequence, so query m sees the tokens below
+   * context_len - (Mq - 1 - m): the bottom-right aligned causal mask of fa_flash_fwd for a short
+   * query block (src/flag_attn/split_kv.py:14-160 serves these shapes in the reference).  For
+   * non-causal attention over several queries leave it 0 and just list the queries as heads. */
+  int32_t causal_rows;
 } fa_paged_args;
 
 /* Token j of sequence i is read at

@@ -122,6 +122,32 @@ def test_total_attention_gqa_and_standalone():
     assert torch.equal(tot, tot2)
 
 
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal", [(2, 4, 2, 700, 900, 128, True), (1, 6, 6, 1300, 1300, 64, True),
+                                                  (2, 4, 1, 513, 257, 128, False), (1, 2, 2, 100, 1030, 64, True),
+                                                  (1, 2, 2, 1030, 100, 128, True), (1, 3, 3, 4224, 4224, 128, True)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_total_attention_on_both_kernel_families(B, Hq, Hk, M, N, D, causal, dtype):
+    """total_attention at head_dim 64 / 128 runs on a tcgen05 kernel (S^T tiles in TMEM, column sums
+    in the element-wise warps); the shape-generic kernel serves the other head sizes.  Both are held
+    to the oracle here: ragged sizes, GQA, M > N (rows without keys), N > M (keys past every query
+    under the causal mask), BTHD strides, and a length with many query tiles per key block."""
+    layout = "BTHD" if (M + N) % 2 else "BHTD"
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 1.0, layout, seed=M + N)
+    ref = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True,
+                                 return_total_attention=True, upcast=True)
+    tor = oracle.flash_attention(q, k, v, causal, return_log_normalizer=True,
+                                 return_total_attention=True, upcast=False)
+    got = {}
+    for family in ("auto", "generic"):
+        with _C.kernel_family(family):
+            _, L, tot, *_ = fa.flash_attention(q, k, v, causal, return_log_normalizer=True,
+                                               return_total_attention=True)
+        assert tot.shape == (B, Hq, N) and tot.dtype == torch.float32
+        assert_within_2x(tot, ref[2], tor[2], f"total_attention ({family})")
+        got[family] = tot
+    assert max_diff(got["auto"], got["generic"]) <= 1e-3 * max(1.0, ref[2].abs().max().item())
+
+
 def test_empty_rows_give_zero_output_and_neg_inf_lse():
     q, k, v, do = make_qkv(1, 2, 2, 100, 10, 64, torch.float16, "cuda", seed=3)
     q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
@@ -332,6 +358,39 @@ def test_a_wait_that_runs_out_poisons_the_status_word_and_the_context_survives()
         assert lib.fa_device_status(ctypes.byref(out), 1) == 0
     assert lib.fa_device_status(ctypes.byref(out), 0) == 0 and out.value == 0
     assert torch.equal(fa.flash_attention(q, k, v, True), o_good)
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D", [(2, 8, 8, 2, 4096, 128), (1, 8, 2, 4, 2048, 64), (2, 4, 4, 16, 8192, 128),
+                                            (1, 16, 2, 8, 1040 * 16, 128), (1, 4, 4, 3, 4112, 32), (3, 2, 1, 5, 1024, 64)])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_few_queries_per_head_through_the_gather_kernel(B, Hq, Hk, M, N, D, causal, dtype):
+    """Inference calls with a handful of queries per head (2 .. 16: speculative decoding, chunked
+    prefill tails), where the reference splits the keys (src/flag_attn/flash.py:59-61), run on the
+    paged-decode kernel with K and V in place: the M queries of a head ride as M rows of its kv
+    head's query tile, each with its own causal limit.  Checked against the oracle, and the
+    dispatch itself is checked (the call must not have gone to the tile kernels)."""
+    from flagattention_b200 import flash as fl_mod
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, "cuda", 1.0, "BHTD", seed=M + N)
+    taken = []
+    real = fl_mod._decode_forward
+
+    def spy(*args, **kw):
+        taken.append(True)
+        return real(*args, **kw)
+    fl_mod._decode_forward = spy
+    try:
+        with torch.no_grad():
+            o = fa.flash_attention(q, k, v, causal)
+    finally:
+        fl_mod._decode_forward = real
+    assert taken, "expected the decode path"
+    o_ref = oracle.flash_attention(q, k, v, causal, upcast=True)
+    o_tor = oracle.flash_attention(q, k, v, causal, upcast=False)
+    assert_within_2x(o, o_ref, o_tor, "o")
+    # the tile kernels (what a call that needs gradients or the log-normaliser gets) agree
+    o2, _lse, *_ = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)
+    assert max_diff(o, o2) <= 4 * 2 ** -8 * max(1.0, o2.float().abs().max().item())
 
 
 def test_device_status_word_is_clean():

@@ -129,7 +129,10 @@ def test_single_query_dispatch_rule():
     k = torch.zeros(2, 2, 1024, 64, dtype=torch.float16)
     v = torch.zeros(2, 2, 1024, 64, dtype=torch.float16)
     assert fl._decode_covered(q, k, v)
-    assert not fl._decode_covered(torch.zeros(2, 8, 2, 64, dtype=torch.float16), k, v)      # M != 1
+    assert fl._decode_covered(torch.zeros(2, 8, 2, 64, dtype=torch.float16), k, v)          # two queries per head
+    assert not fl._decode_covered(torch.zeros(2, 8, 17, 64, dtype=torch.float16), k, v)     # 4 x 17 rows per kv head
+    assert fl._decode_covered(torch.zeros(2, 8, 16, 64, dtype=torch.float16), k, v, True)   # causal, M <= N
+    assert not fl._decode_covered(torch.zeros(2, 8, 16, 64, dtype=torch.float16), k[:, :, :0], v[:, :, :0])
     assert not fl._decode_covered(q, k[:, :, :1000], v[:, :, :1000])                        # N % 16 != 0
     kt = torch.zeros(2, 1024, 2, 64, dtype=torch.float16).transpose(1, 2)                   # BTHD view
     assert fl._decode_covered(q, kt, kt.clone(memory_format=torch.preserve_format))

@@ -579,6 +579,37 @@ def run_piecewise(args, dist, rank, world, device, sampler):
     return rec
 
 
+def run_total(args, dist, rank, world, device):
+    """total_attention (the column sums of the attention matrix, recomputed from the log-normaliser)
+    at config 3's shape: one score product and one exponential per score on the tcgen05 kernel."""
+    import flagattention_b200 as fa
+    from flagattention_b200.total import total_attention
+    c = CFG3
+    B, H, L, D = c["B"], c["H"], c["L"], c["D"]
+    gen = torch.Generator(device=device).manual_seed(10086 + 8 + rank)
+    q, k, v = ((torch.randn((B, H, L, D), generator=gen, device=device) * 0.5).to(torch.float16) for _ in range(3))
+    _, lse, *_ = fa.flash_attention(q, k, v, causal=False, return_log_normalizer=True)
+    steps = max(args.steps, 10)
+    own = ClockSampler(device.index)
+    own.start()
+    ms, _ = timed(lambda: total_attention(q, k, lse, causal=False), steps, dist, device, warm=3, warm_seconds=0.3)
+    t1 = time.time()
+    own.stop()
+    clocks = own.window(t1 - steps * ms * 1e-3 - 0.002, t1)
+    mhz = clocks.get("sm_mhz") or 1965.0
+    flop = 2.0 * B * H * L * L * D
+    scores = float(B) * H * L * L
+    return dict(metric="total_attention TFLOP/s (one score product per pair; hd64 non-causal fp16)",
+                value=round(world * flop / (ms * 1e-3) / 1e12, 2), unit="TFLOP/s", ms_per_step=round(ms, 4),
+                steps=steps, config=dict(workload="total_attention fp16, device-resident", **c),
+                roofline=tensor_roofline("total_attention_tc_kernel", flop, ms, clocks=clocks,
+                                         ex2=dict(note="one ex2 per score; peak = 16 / clk / SM x 148 SMs at the sampled clock: "
+                                                       "the unit that bounds this kernel",
+                                                  sm_mhz=mhz,
+                                                  frac=round(scores / (ms * 1e-3) / (EX2_PER_CLK_PER_SM * SM_COUNT * mhz * 1e6), 4))),
+                clocks=clocks, gpu_launches=steps)
+
+
 def run_sweep(args, dist, rank, world, device):
     """Forward and backward TFLOP/s over the sequence lengths of the reference's benchmark grid
     (benchmark/flash_benchmark.py there: batch = 32768 / L, heads = 2048 / D, causal, bf16), a few
@@ -936,7 +967,11 @@ def main():
     ap.add_argument("--e2e-heads", type=int, default=8, help="heads per chunk of the host-buffer pipeline")
     ap.add_argument("--skip-piecewise", action="store_true")
     ap.add_argument("--skip-extras", action="store_true", help="no cfg3 / sweep / decode / rotary / strong records")
-    ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise", "rotary", "cfg3", "sweep"],
+    ap.add_argument("--backward", default="auto", choices=["auto", "one_pass", "two_kernel"],
+                    help="backward kernels of the dense operators (flagattention_b200.flash.set_backward_mode)")
+    ap.add_argument("--kernels", default="auto", choices=["auto", "generic"],
+                    help="generic: the shape-generic mma.sync kernels instead of the tcgen05 ones (profiling)")
+    ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise", "rotary", "cfg3", "sweep", "total"],
                     help="run one workload only (profiling); the JSON line is then partial")
     ap.add_argument("--paged-seqs", type=int, default=PAGED_CFG["num_seqs"],
                     help="number of sequences of the paged workload (smaller for profiler captures)")
@@ -954,13 +989,18 @@ def main():
     torch.cuda.set_device(device)
     sampler = ClockSampler(local)
     sampler.start()
+    from flagattention_b200 import _C as fa_c
+    from flagattention_b200 import flash as fa_flash
+    fa_flash.set_backward_mode(args.backward)
+    fa_c.load().fa_set_kernel_family(1 if args.kernels == "generic" else 0)
 
     PAGED_CFG["num_seqs"] = args.paged_seqs
     single = {"paged": lambda: run_paged(args, dist, rank, world, device),
               "rotary": lambda: run_rotary(args, dist, rank, world, device),
               "piecewise": lambda: run_piecewise(args, dist, rank, world, device, sampler),
               "cfg3": lambda: run_cfg3(args, dist, rank, world, device, sampler),
-              "sweep": lambda: run_sweep(args, dist, rank, world, device)}
+              "sweep": lambda: run_sweep(args, dist, rank, world, device),
+              "total": lambda: run_total(args, dist, rank, world, device)}
     if args.only in single:
         rec = single[args.only]()
         sampler.stop()
@@ -979,6 +1019,7 @@ def main():
     sweep = run_sweep(args, dist, rank, world, device) if extras else None
     dec = run_decode(args, dist, rank, world, device) if extras and not args.skip_paged else None
     rot = run_rotary(args, dist, rank, world, device) if extras else None
+    tot = run_total(args, dist, rank, world, device) if extras else None
     sampler.stop()
     cpu = None
     if rank == 0 and not args.skip_cpu and world == 1:
@@ -1022,7 +1063,7 @@ def main():
                                  "K timed steps, no idle gap; CUDA events, slowest rank"},
             "roofline": fl["roofline"], "cpu_baseline": cpu, "e2e": fl["e2e"],
             "gpu_launches": fl["launches"], "clocks": clocks, "paged": paged, "strong": strong,
-            "cfg3": cfg3, "piecewise": pw, "sweep": sweep, "decode": dec, "rotary": rot,
+            "cfg3": cfg3, "piecewise": pw, "sweep": sweep, "decode": dec, "rotary": rot, "total": tot,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

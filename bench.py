@@ -40,6 +40,8 @@ import time
 
 import torch
 
+_T0 = time.perf_counter()
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -181,6 +183,12 @@ def dist_setup():
     return None, 0, 1, 0
 
 
+def trace(rank, what):
+    """Progress marks on stderr (rank 0): if a run is cut short, the log says where it was."""
+    if rank == 0:
+        print("[bench %.1fs] %s" % (time.perf_counter() - _T0, what), file=sys.stderr, flush=True)
+
+
 def max_over_ranks(dist, value, device):
     if dist is None:
         return value
@@ -199,12 +207,21 @@ def timed(fn, steps, dist, device, warm=3, warm_seconds=0.0):
     """`warm` untimed calls (continued until `warm_seconds` of load), then, after a barrier among the
     ranks and with no idle gap on this GPU, `steps` timed calls; returns (ms per call, max over
     ranks; per-call device times of this rank)."""
+    # The number of warm-up calls must be the same on every rank (fn may hold a collective): each
+    # rank proposes a count from its own pace, the largest wins.
     t_w = time.perf_counter()
-    done = 0
-    while done < warm or time.perf_counter() - t_w < warm_seconds:
+    for _ in range(warm):
         fn()
-        done += 1
-        if done % 8 == 0:
+    extra = 0
+    if warm_seconds > 0.0:
+        torch.cuda.synchronize()
+        spent = time.perf_counter() - t_w
+        if spent < warm_seconds:
+            extra = int((warm_seconds - spent) / max(spent / max(warm, 1), 1e-5)) + 1
+        extra = int(max_over_ranks(dist, float(extra), device))
+    for i in range(extra):
+        fn()
+        if i % 8 == 7:
             torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()       # enqueued behind the warm-up: the GPU goes straight on to the timed calls
@@ -432,6 +449,7 @@ def run_flash(args, dist, rank, world, device, sampler):
                roofline=roofline, e2e=None, windows=dict(timed=timed_window, staged=(t_wall1, t_staged1),
                                                          sustained=(t_sus0, t_sus1), all=(t_wall0, t_sus1)),
                launches=len([n for n in per_kernel if n != "dq_zero"]) * args.steps, numa=numa)
+    trace(rank, "flash: device-resident legs done")
     if args.skip_e2e:
         prefer_host_memory_near_gpu(device.index, on=False)
         return out
@@ -450,8 +468,10 @@ def run_flash(args, dist, rank, world, device, sampler):
     e2e_step = pipelined_e2e(host, outs_host, chunks, lambda t, ch: t[ch[0]:ch[0] + 1, ch[1]:ch[1] + HG],
                              compute, device)
     e2e_ms, e2e_step_ms = timed(e2e_step, e2e_steps, dist, device, warm=3)
+    trace(rank, "flash: end-to-end leg done")
     nbytes = B * H * L * D * 2
     ceil_gbs, ceil_ms = copy_ceiling(device, 4 * nbytes, dist)
+    trace(rank, "flash: copy ceiling done")
     out["e2e"] = dict(
         value=round(world * (fwd_f + bwd_f) / (e2e_ms * 1e-3) / 1e12, 2), unit="TFLOP/s",
         ms_per_step=round(e2e_ms, 3), h2d_bytes_per_step=4 * nbytes, d2h_bytes_per_step=4 * nbytes,
@@ -828,6 +848,7 @@ def run_strong(args, dist, rank, world, device):
                               "pairs; no exchange (dq, dk, dv of a pair stay with the pair)")
     del q, k, v, do
     torch.cuda.empty_cache()
+    trace(rank, "strong: dense done")
 
     # ---- decode: the 64 sequences by longest-first assignment, outputs all-gathered ---------------
     pc = PAGED_CFG
@@ -1008,10 +1029,14 @@ def main():
             print(json.dumps({"partial": True, args.only: rec}), flush=True)
         return
 
+    trace(rank, "process group up, %d rank(s)" % world)
     fl = run_flash(args, dist, rank, world, device, sampler)
+    trace(rank, "flash done")
     flash_only = args.only == "flash"
     paged = None if (args.skip_paged or flash_only) else run_paged(args, dist, rank, world, device)
+    trace(rank, "paged done")
     strong = None if (args.skip_extras or flash_only) else run_strong(args, dist, rank, world, device)
+    trace(rank, "strong-scaling records done")
     # the secondary records are single-GPU measurements
     extras = world == 1 and not flash_only and not args.skip_extras
     pw = run_piecewise(args, dist, rank, world, device, sampler) if (world == 1 and not flash_only and not args.skip_piecewise) else None

@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = (
     "fa_paged_decode", "fa_paged_reduce", "fa_paged_workspace_bytes", "fa_paged_trace_blocks",
     "fa_paged_attention_noalloc", "fa_dropout_mask",
     "fa_flash_bwd_fused", "fa_flash_bwd_fused_stages", "fa_flash_bwd_fused_workspace_bytes", "fa_piecewise_bwd_fused",
+    "fa_piecewise_bwd_fused_workspace_bytes",
     "fa_paged_cache_append", "fa_rotary_pair_fwd", "fa_rotary_pair_bwd",
     "fa_device_status", "fa_debug_wait_probe", "fa_set_kernel_family", "fa_status_string", "fa_version",
 )
@@ -82,6 +83,7 @@ def load():
             lib.fa_splitkv_workspace_bytes.restype = ctypes.c_int64
             lib.fa_paged_workspace_bytes.restype = ctypes.c_int64
             lib.fa_flash_bwd_fused_workspace_bytes.restype = ctypes.c_int64
+            lib.fa_piecewise_bwd_fused_workspace_bytes.restype = ctypes.c_int64
             lib.fa_num_splits_heuristic.restype = ctypes.c_int32
             lib.fa_num_splits_heuristic.argtypes = [ctypes.c_int32] * 8
             lib.fa_debug_wait_probe.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]

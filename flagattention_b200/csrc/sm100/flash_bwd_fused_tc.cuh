@@ -72,8 +72,10 @@ enum FusedBar { FB_KV_FULL = 0, FB_Q_FULL = 1, FB_Q_FREE = 3, FB_DO_FULL = 5, FB
                 FB_ITEM_FULL = 26 /* .. 29 */, FB_DQ_HALF = 30 };
 
 struct FusedBwdParams {
-  BwdTcParams base;
+  BwdTcParams base;   // base.mode: 0 = flash_attention, 3 = piecewise_attention (both branches)
   float *dq_acc;      // (B, H, Mpad / 128, D / 4, 128, 4) fp32, zeroed before the launch
+  float *dq_acc2;     // piecewise: the same for dq2 (far branch); dq_acc then holds dq1
+  void *dk2;          // piecewise: dk of the far branch (base.dk: near branch), same strides
   int Mpad;           // M rounded up to a multiple of 128
   unsigned *sched;    // work-item counter; zero at launch and at exit (see the kernel)
   int num_items;      // key blocks x (batch, kv head) pairs
@@ -132,8 +134,15 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t sm
 constexpr int kFusedThreads = kBwdThreads + 5 * 32;   // 736
 
 // One work item = one block of 128 keys of one (batch, kv head) pair: its query-tile range.
+// Under piecewise_attention a block is walked twice, back to back by the same CTA: first the
+// tiles that hold a near pair (mode 1: q1, k1 -> dq1, dk1), then the tiles that hold a far pair
+// (mode 2: q2, k2 -> dq2, dk2).  V stays in shared memory and dV keeps accumulating in TMEM
+// across the two walks (`first` / `last`: the walk opens / closes the block), so dV is rounded
+// once and V and dO of a straddling tile are not fetched by a second launch.
 struct FusedItem {
   int n0, hk, b, mt_lo, mt_hi, T_tiles;
+  int mode;          // 0 flash, 1 near walk, 2 far walk
+  bool first, last;  // of its key block's walks (those with tiles)
 };
 
 // PERSISTENT: the grid is one CTA per SM.  A CTA works through items (key block, pair) in the
@@ -153,7 +162,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                               const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v,
                               const __grid_constant__ CUtensorMap map_dk,
-                              const __grid_constant__ CUtensorMap map_dv, const FusedBwdParams fp) {
+                              const __grid_constant__ CUtensorMap map_dv,
+                              const __grid_constant__ CUtensorMap map_q2,    // far walk (piecewise); else = map_q ...
+                              const __grid_constant__ CUtensorMap map_k2,
+                              const __grid_constant__ CUtensorMap map_dk2, const FusedBwdParams fp) {
   using C = FusedBwdCfg<D>;
   constexpr int BM = C::BM, BN = C::BN, KSUB = C::KSUB, NQ = C::NQ, NDO = C::NDO;
   const BwdTcParams &p = fp.base;
@@ -173,27 +185,41 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   const int total = fp.num_items;
 
   // query tiles [mt_lo, mt_hi) that the key block starting at n0 walks
-  auto tile_range = [&](int n0, int &mt_lo, int &mt_hi) {
+  auto tile_range = [&](int n0, int mode, int &mt_lo, int &mt_hi) {
     mt_lo = 0;
     if (p.causal) mt_lo = max(0, n0 - p_seq) / BM;
     mt_hi = num_m_tiles;
-    if (p.mode == 1) {  // query tiles that hold a near pair
+    if (mode == 1) {  // query tiles that hold a near pair
       const int lim = p.w - p_seq + n0 + BN - 1;
       mt_hi = min(mt_hi, lim <= 0 ? 0 : (lim + BM - 1) / BM);
-    } else if (p.mode == 2) {  // query tiles that hold a far pair
+    } else if (mode == 2) {  // query tiles that hold a far pair
       const int lim = p.w - p_seq + n0 - (BM - 1);
       mt_lo = max(mt_lo, lim <= 0 ? 0 : (lim + BM - 1) / BM);
     }
   };
-  auto decode = [&](int w) -> FusedItem {
-    const CtaCoord cta = grouped_cta((unsigned)w, p.num_blocks, p.B * p.Hk, p.group_size);
+  // Walk ids: flash_attention has one walk per key block (id = position of the block in the order
+  // of grouped_cta()); piecewise_attention two (id = 2 * position + walk: 0 near, 1 far).
+  const bool pw = (p.mode == 3);
+  const int end_id = pw ? 2 * total : total;
+  auto decode = [&](int id) -> FusedItem {
+    const int unit = pw ? (id >> 1) : id;
+    const CtaCoord cta = grouped_cta((unsigned)unit, p.num_blocks, p.B * p.Hk, p.group_size);
     FusedItem it;
     it.n0 = cta.blk * BN, it.hk = cta.pair % p.Hk, it.b = cta.pair / p.Hk;
-    tile_range(it.n0, it.mt_lo, it.mt_hi);
+    it.mode = pw ? 1 + (id & 1) : p.mode;
+    tile_range(it.n0, it.mode, it.mt_lo, it.mt_hi);
     it.T_tiles = max(0, it.mt_hi - it.mt_lo) * G;
+    it.first = it.last = true;
+    if (pw) {
+      int lo, hi;
+      tile_range(it.n0, 3 - it.mode, lo, hi);
+      const bool other = hi > lo;            // the block's other walk has tiles too
+      if (it.mode == 1) it.last = !other;
+      else it.first = !other;
+    }
     return it;
   };
-  // the id of this CTA's `ic`-th item, as published by the producer thread (>= total: no more)
+  // the id of this CTA's `ic`-th item, as published by the producer thread (>= end_id: no more)
   auto ring_item = [&](int ic, int where) -> int {
     if (!mbar_wait(bar(FB_ITEM_FULL + (ic & 3)), (ic >> 2) & 1, actx, where)) return -1;
     return item_ring[ic & 3];
@@ -201,17 +227,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) return;
 
-  // Next work item with at least one tile, starting at w: items past the end of the list (>= total)
-  // end the CTA.  Every id beyond the CTA's first comes from the global counter; whoever makes the
+  // First walk with at least one tile of key block `unit` or, if it has none, of the next block
+  // handed out: blocks past the end of the list (>= total) end the CTA (returns end_id).  Every id beyond the CTA's first comes from the global counter; whoever makes the
   // last fetch of the launch (every CTA ends on exactly one fetch past the end, so there are `total`
   // in all) puts the counter back to zero for the next launch.
-  auto next_real = [&](int w) -> int {
-    while (w < total && decode(w).T_tiles == 0) {
+  auto first_walk_of = [&](int unit) -> int {
+    while (unit < total) {
+      if (!pw) {
+        if (decode(unit).T_tiles > 0) return unit;
+      } else {
+        if (decode(2 * unit).T_tiles > 0) return 2 * unit;
+        if (decode(2 * unit + 1).T_tiles > 0) return 2 * unit + 1;
+      }
       const unsigned fetched = atomicAdd(fp.sched, 1u);
       if (fetched == (unsigned)total - 1u) atomicExch(fp.sched, 0u);
-      w = (int)gridDim.x + (int)fetched;
+      unit = (int)gridDim.x + (int)fetched;
     }
-    return w;
+    return end_id;
   };
   int w_first = 0;   // producer thread only
   if (tid == 0) {
@@ -245,7 +277,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     mbar_init(bar(FB_PD_STORED), 1);
     for (int s = 0; s < 4; ++s) mbar_init(bar(FB_ITEM_FULL + s), 1);
     fence_barrier_init();
-    w_first = next_real((int)blockIdx.x);   // the grid never exceeds the number of items
+    w_first = first_walk_of((int)blockIdx.x);   // the grid never exceeds the number of key blocks
     item_ring[0] = w_first;
     mbar_arrive(bar(FB_ITEM_FULL + 0));
     // The loads of the first tile go out right here, before the TMEM allocation and the CTA-wide
@@ -257,15 +289,21 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     tma_prefetch_desc(&map_do);
     tma_prefetch_desc(&map_dk);
     tma_prefetch_desc(&map_dv);
-    if (w_first < total) {
+    if (pw) {
+      tma_prefetch_desc(&map_q2);
+      tma_prefetch_desc(&map_k2);
+      tma_prefetch_desc(&map_dk2);
+    }
+    if (w_first < end_id) {
       const FusedItem first = decode(w_first);
       const int h0 = first.hk * G, m00 = first.mt_lo * BM;
+      const CUtensorMap *mk = first.mode == 2 ? &map_k2 : &map_k, *mq = first.mode == 2 ? &map_q2 : &map_q;
       mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, first.n0, first.hk, first.b);
+        tma_load_4d(smem + C::kK + s * BN * 128, mk, bar(FB_KV_FULL), s * 64, first.n0, first.hk, first.b);
       mbar_expect_tx(bar(FB_Q_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
-        tma_load_4d(smem + C::kQ0 + s * BM * 128, &map_q, bar(FB_Q_FULL), s * 64, m00, h0, first.b);
+        tma_load_4d(smem + C::kQ0 + s * BM * 128, mq, bar(FB_Q_FULL), s * 64, m00, h0, first.b);
       mbar_expect_tx(bar(FB_V_FULL), C::kTile);
       for (int s = 0; s < KSUB; ++s)
         tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, first.n0, first.hk, first.b);
@@ -292,12 +330,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       int real = 0;                           // items with tiles handled so far
       uint32_t gt = 0;                        // tiles of those items
       bool pending = false;                   // dV / dK of the previous such item not stored yet
-      int pn0 = 0, phk = 0, pb = 0;           // its coordinates
+      int pn0 = 0, phk = 0, pb = 0;           // its coordinates,
+      int pmode = 0;                          // its walk
+      bool plast = true;                      // and whether it closed its key block (dV final)
+      int nvl = 0;                            // V tiles requested so far: the phase of V_FULL
       auto load_q = [&](const FusedItem &it, int h, int mt) {
         mbar_expect_tx(bar(FB_Q_FULL + sq), C::kTile);
         for (int s = 0; s < KSUB; ++s)
-          tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, &map_q, bar(FB_Q_FULL + sq),
-                      s * 64, mt * BM, h, it.b);
+          tma_load_4d(smem + C::kQ0 + sq * C::kTile + s * BM * 128, it.mode == 2 ? &map_q2 : &map_q,
+                      bar(FB_Q_FULL + sq), s * 64, mt * BM, h, it.b);
         ++inflight_q;
       };
       auto load_do = [&](const FusedItem &it, int h, int mt) {
@@ -311,7 +352,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       // warps have staged them; `between` runs after the dV store has been requested
       auto store_dv = [&]() -> bool {
         if (!mbar_wait(bar(FB_DV_STAGED), (real - 1) & 1, actx, 721)) return false;
-        if (!p.dv_accumulate) {
+        if (plast && !p.dv_accumulate) {   // a near walk that a far walk follows stages nothing
 #pragma unroll
           for (int s = 0; s < KSUB; ++s)
             tma_store_4d(&map_dv, smem + C::kV + s * BN * 128, s * 64, pn0, phk, pb);
@@ -323,17 +364,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         if (!mbar_wait(bar(FB_DK_STAGED), (real - 1) & 1, actx, 722)) return false;
 #pragma unroll
         for (int s = 0; s < KSUB; ++s)
-          tma_store_4d(&map_dk, smem + C::kPD + s * BN * 128, s * 64, pn0, phk, pb);
+          tma_store_4d(pmode == 2 ? &map_dk2 : &map_dk, smem + C::kPD + s * BN * 128, s * 64, pn0, phk, pb);
         bulk_commit();
         return true;
       };
       int w = w_first, ic = 0;
-      while (w < total && ok) {
-        // ask for the id of the next item now; the answer is looked at after this item's first
-        // loads have gone out, so its latency hides behind them
-        const unsigned fetched = atomicAdd(fp.sched, 1u);
-        int w_next = total;
+      if (w < end_id) nvl = 1;   // V of the first walk: see set-up
+      while (w < end_id && ok) {
         const FusedItem it = decode(w);
+        // Unless the far walk of the same key block follows, ask for the next block now; the answer
+        // is looked at after this walk's first loads have gone out, so its latency hides behind them
+        const bool more = pw && !it.last;
+        const unsigned fetched = more ? 0u : atomicAdd(fp.sched, 1u);
+        int w_next = end_id;
         {
           int h = it.hk * G, mt = it.mt_lo;
           const bool preissued = (ic == 0);   // tile 0, K and V of the first item: see set-up
@@ -356,25 +399,33 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             }
             mbar_expect_tx(bar(FB_KV_FULL), C::kTile);
             for (int s = 0; s < KSUB; ++s)
-              tma_load_4d(smem + C::kK + s * BN * 128, &map_k, bar(FB_KV_FULL), s * 64, it.n0, it.hk, it.b);
+              tma_load_4d(smem + C::kK + s * BN * 128, it.mode == 2 ? &map_k2 : &map_k, bar(FB_KV_FULL),
+                          s * 64, it.n0, it.hk, it.b);
             if (pending) {
               ok = store_dk();
               if (!ok) break;
-              bulk_wait_read_1();            // the dV store has read the shared memory of V
+              bulk_wait_read_1();            // the dV store (if any) has read the shared memory of V
             }
-            mbar_expect_tx(bar(FB_V_FULL), C::kTile);
-            for (int s = 0; s < KSUB; ++s)
-              tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, it.n0, it.hk, it.b);
+            if (it.first) {                  // a far walk after a near one finds V in place
+              mbar_expect_tx(bar(FB_V_FULL), C::kTile);
+              for (int s = 0; s < KSUB; ++s)
+                tma_load_4d(smem + C::kV + s * BN * 128, &map_v, bar(FB_V_FULL), s * 64, it.n0, it.hk, it.b);
+              ++nvl;
+            }
             if (pending) {
               bulk_wait_read_all();          // the dK store has read the P^T / dS^T tile
               mbar_arrive(bar(FB_PD_STORED));
             }
           }
-          pending = true, pn0 = it.n0, phk = it.hk, pb = it.b;
+          pending = true, pn0 = it.n0, phk = it.hk, pb = it.b, pmode = it.mode, plast = it.last;
           ++real;
-          // hand the next item's id to the other warps
-          if (fetched == (unsigned)total - 1u) atomicExch(fp.sched, 0u);
-          w_next = next_real((int)gridDim.x + (int)fetched);
+          // hand the next walk's id to the other warps
+          if (more) {
+            w_next = w + 1;
+          } else {
+            if (fetched == (unsigned)total - 1u) atomicExch(fp.sched, 0u);
+            w_next = first_walk_of((int)gridDim.x + (int)fetched);
+          }
           item_ring[(ic + 1) & 3] = w_next;
           mbar_arrive(bar(FB_ITEM_FULL + ((ic + 1) & 3)));
           if (++sq == NQ) sq = 0, phq ^= 1;
@@ -395,11 +446,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           gt += (uint32_t)it.T_tiles;
           // K and V of the next item are read by nobody else: start them towards L2 now, a couple
           // of tiles before this item ends (any earlier and they would be evicted again)
-          if (w_next < total) {
+          if (w_next < end_id) {
             const FusedItem nx = decode(w_next);
             for (int s = 0; s < KSUB; ++s) {
-              tma_prefetch_l2_4d(&map_k, s * 64, nx.n0, nx.hk, nx.b);
-              tma_prefetch_l2_4d(&map_v, s * 64, nx.n0, nx.hk, nx.b);
+              tma_prefetch_l2_4d(nx.mode == 2 ? &map_k2 : &map_k, s * 64, nx.n0, nx.hk, nx.b);
+              if (nx.first) tma_prefetch_l2_4d(&map_v, s * 64, nx.n0, nx.hk, nx.b);
             }
           }
         }
@@ -417,10 +468,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
           while (!mbar_try_wait(bar(FB_Q_FULL + i % NQ), (i / NQ) & 1) && clock64() - t0 < 2000000) {}
         for (int i = max(0, inflight_do - NDO); i < inflight_do; ++i)
           while (!mbar_try_wait(bar(FB_DO_FULL + i % NDO), (i / NDO) & 1) && clock64() - t0 < 2000000) {}
-        if (real > 0) {
+        if (real > 0)
           while (!mbar_try_wait(bar(FB_KV_FULL), (real - 1) & 1) && clock64() - t0 < 2000000) {}
-          while (!mbar_try_wait(bar(FB_V_FULL), (real - 1) & 1) && clock64() - t0 < 2000000) {}
-        }
+        if (nvl > 0)
+          while (!mbar_try_wait(bar(FB_V_FULL), (nvl - 1) & 1) && clock64() - t0 < 2000000) {}
       }
     }
   } else if (warp == 1) {
@@ -454,6 +505,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       bool ok = true;
       int sq = 0, phq = 0, sd = 0, phd = 0;
       int real = 0;            // items with tiles so far
+      int nv = 0;              // V tiles so far: the phase of V_FULL (a far walk after a near one loads none)
       uint32_t gt = 0;         // tiles so far, over all items: the phase of every per-tile barrier
       uint32_t gh = 0;         // dQ parts so far: the phase of DQ_FULL / DQ_FREE
       // part `hf` of dQ = dS K into the dQ columns, a fresh accumulator: the read-out of the part
@@ -473,7 +525,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
       };
       for (int ic = 0; ok; ++ic) {
         const int w = ring_item(ic, 801);
-        if (w < 0 || w >= total) break;
+        if (w < 0 || w >= end_id) break;
         const FusedItem it = decode(w);
         ok = mbar_wait(bar(FB_KV_FULL), real & 1, actx, 811);
         // the score columns still hold dP^T of the previous item's last tile until the
@@ -486,11 +538,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         for (int t = 0; t < it.T_tiles && ok; ++t, ++gt) {
           int nsq = sq + 1, nphq = phq;
           if (nsq == NQ) nsq = 0, nphq ^= 1;
-          const uint32_t acc = t > 0 ? 1u : 0u;
+          const uint32_t acc = t > 0 ? 1u : 0u;                  // dK: fresh per walk
+          const uint32_t acc_dv = (t > 0 || !it.first) ? 1u : 0u;   // dV: fresh per key block
           const uint32_t par = gt & 1;
           // dP^T(t) = V dO^T over S^T(t), once every element-wise warp holds S^T(t) in registers
           ok = mbar_wait(bar(FB_S_LOADED), par, actx, 813);
-          if (ok && t == 0) ok = mbar_wait(bar(FB_V_FULL), real & 1, actx, 820);
+          if (ok && t == 0 && it.first) ok = mbar_wait(bar(FB_V_FULL), (nv++) & 1, actx, 820);
           if (ok) ok = mbar_wait(bar(FB_DO_FULL + sd), phd, actx, 814);
           if (!ok) break;
           tc_fence_after();
@@ -519,7 +572,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 #pragma unroll
             for (int kk = 0; kk < BM / 16; ++kk)
               mma_ts_lo(tmem + C::kColDV, tmem + C::kColP + kk * 8, b_lo + ((kk * 16 * 128) >> 4),
-                        idesc_acc, kk > 0 ? 1u : acc);
+                        idesc_acc, kk > 0 ? 1u : acc_dv);
             mma_commit(bar(FB_DO_FREE + sd));
             mma_commit(bar(FB_PT_FREE));
           }
@@ -576,7 +629,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     uint32_t gt = 0;
     for (int ic = 0; ok; ++ic) {
       const int w = ring_item(ic, 950);
-      if (w < 0 || w >= total) break;
+      if (w < 0 || w >= end_id) break;
       const FusedItem it = decode(w);
       int h = it.hk * G, mt = it.mt_lo;
       for (int t = 0; t < it.T_tiles; ++t, ++gt) {
@@ -629,12 +682,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         ok = false;
         break;
       }
-      if (w >= total) break;
+      if (w >= end_id) break;
       const FusedItem it = decode(w);
       int h = it.hk * G, mt = it.mt_lo;
       for (int t = 0; t < it.T_tiles; ++t, ++gt) {
         // the tile's block of the workspace: D / 4 runs of (128 queries x 4 columns), contiguous
-        float *dst = fp.dq_acc + (((int64_t)it.b * p.H + h) * (fp.Mpad / BM) + mt) * (int64_t)(BM * D);
+        float *dst = (it.mode == 2 ? fp.dq_acc2 : fp.dq_acc) +
+                     (((int64_t)it.b * p.H + h) * (fp.Mpad / BM) + mt) * (int64_t)(BM * D);
         if (++mt == it.mt_hi) mt = it.mt_lo, ++h;
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd) {
@@ -729,7 +783,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     for (int ic = 0; ok; ++ic) {
       const int w = ring_item(ic, 900);
       ok = __all_sync(0xffffffffu, w >= 0);
-      if (!ok || w >= total) break;
+      if (!ok || w >= end_id) break;
       const FusedItem it = decode(w);
       const int n0 = it.n0, key = n0 + row;
       const bool key_ok = key < p.N;
@@ -771,13 +825,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         // masking at all; the others mask with one unsigned range check per element:
         // column c is visible iff cmin <= c < cmin + cwidth.
         bool interior = (n0 + BN <= p.N) && (!p.causal || m0 + p_seq >= n0 + BN - 1);
-        if (p.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
-        if (p.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
+        if (it.mode == 1) interior = interior && (m0 + BM - 1 + p_seq - n0 < p.w);
+        if (it.mode == 2) interior = interior && (m0 + p_seq - (n0 + BN - 1) >= p.w);
         int cmin = 0, cmax = 32;
         if (p.causal) cmin = max(cmin, key - p_seq - m0 - cg * 32);
-        if (p.mode) {
+        if (it.mode) {
           const int cnear = p.w + key - p_seq - m0 - cg * 32;  // columns below it are near pairs
-          if (p.mode == 1) cmax = min(cmax, cnear);
+          if (it.mode == 1) cmax = min(cmax, cnear);
           else cmin = max(cmin, cnear);
         }
         if (!key_ok) cmin = 32;
@@ -892,12 +946,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        load_cols(C::kColDV, ov);
-        if (!p.dv_accumulate) {
-          stage(C::kV, ov, 1.f);
-          fence_proxy_async_smem();
-        } else {
-          direct(p.dv, p.sdv, ov, 1.f, true);
+        if (it.last) {   // (a near walk that a far walk follows leaves dV in TMEM and V in place)
+          load_cols(C::kColDV, ov);
+          if (!p.dv_accumulate) {
+            stage(C::kV, ov, 1.f);
+            fence_proxy_async_smem();
+          } else {
+            direct(p.dv, p.sdv, ov, 1.f, true);
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(FB_DV_STAGED));

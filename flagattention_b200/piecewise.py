@@ -71,10 +71,11 @@ class PiecewiseAttention(torch.autograd.Function):
             dk1 = torch.empty(k1.shape, dtype=k1.dtype, device=k1.device)
             dk2 = torch.empty(k2.shape, dtype=k2.dtype, device=k2.device)
             dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-            ws_bytes = (lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
+            ws_bytes = (lib.fa_piecewise_bwd_fused_workspace_bytes(_C.byref(shape))
                         if use_one_pass_backward() else 0)
             if ws_bytes > 0:
-                # one pass per branch over the score tiles; dq1 / dq2 accumulate in an fp32 workspace
+                # one launch: every key block walks its near tiles, then its far tiles; dq1 / dq2
+                # accumulate in two fp32 workspaces, dV in TMEM across both walks
                 dq1 = torch.empty(q1.shape, dtype=q1.dtype, device=q1.device)
                 dq2 = torch.empty(q2.shape, dtype=q2.dtype, device=q2.device)
                 ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q1.device)

@@ -193,11 +193,15 @@ int fa_flash_bwd_fused_stages(const fa_flash_shape *s, const fa_tensor4 *q, cons
                               const fa_tensor4 *dv, void *workspace, int64_t workspace_bytes,
                               int32_t stages, void *stream);
 
-/* All five gradients of piecewise_attention from one pass per branch over the score tiles: the
- * counterpart of fa_flash_bwd_fused (same workspace size, from fa_flash_bwd_fused_workspace_bytes
- * on the same shape; 0 = not covered, use fa_piecewise_bwd_dkdv + fa_piecewise_bwd_dq).
- * Replaces the pair of launches at src/flag_attn/piecewise.py:114-164.  dq1, dq2 are
- * reproducible to fp32 rounding only. */
+/* All five gradients of piecewise_attention from ONE launch: the counterpart of
+ * fa_flash_bwd_fused.  Every block of 128 keys is walked twice by the same CTA, first over the
+ * query tiles that hold a near pair (q1.k1 -> dq1, dk1), then over those that hold a far pair
+ * (q2.k2 -> dq2, dk2); V stays in shared memory and dV accumulates in fp32 across both walks, so
+ * it is rounded once.  The workspace holds two dq accumulators:
+ * fa_piecewise_bwd_fused_workspace_bytes on the same shape (0 = not covered, use
+ * fa_piecewise_bwd_dkdv + fa_piecewise_bwd_dq).  Replaces the pair of launches at
+ * src/flag_attn/piecewise.py:114-164.  dq1, dq2 are reproducible to fp32 rounding only. */
+int64_t fa_piecewise_bwd_fused_workspace_bytes(const fa_flash_shape *s);
 int fa_piecewise_bwd_fused(const fa_flash_shape *s, int32_t dist_threshold, const fa_tensor4 *q1,
                            const fa_tensor4 *k1, const fa_tensor4 *q2, const fa_tensor4 *k2,
                            const fa_tensor4 *v, const fa_tensor4 *d_o, const float *lse,

@@ -60,6 +60,11 @@ def test_one_pass_backward_and_cache_writer_validation_needs_no_gpu(built_lib):
     shape = _C.FlashShape(_C.FA_BF16, 2, 4, 2, 300, 500, 128, 1, 0.1)
     # (B, H, ceil(M / 128) * 128, D) fp32 + 16 bytes for the work-item counter
     assert lib.fa_flash_bwd_fused_workspace_bytes(ctypes.byref(shape)) == 2 * 4 * 384 * 128 * 4 + 16
+    # piecewise: two accumulators (dq1, dq2); needs as many kv heads as query heads
+    lib.fa_piecewise_bwd_fused_workspace_bytes.restype = ctypes.c_int64
+    assert lib.fa_piecewise_bwd_fused_workspace_bytes(ctypes.byref(shape)) == 0
+    mha = _C.FlashShape(_C.FA_BF16, 2, 4, 4, 300, 500, 128, 1, 0.1)
+    assert lib.fa_piecewise_bwd_fused_workspace_bytes(ctypes.byref(mha)) == 2 * (2 * 4 * 384 * 128 * 4) + 16
     small = _C.FlashShape(_C.FA_BF16, 2, 4, 2, 300, 500, 32, 1, 0.1)       # head_dim 32: two-kernel path only
     assert lib.fa_flash_bwd_fused_workspace_bytes(ctypes.byref(small)) == 0
     drop = _C.FlashShape(_C.FA_BF16, 2, 4, 2, 300, 500, 128, 1, 0.1, 0.5, 1, 0)   # dropout: not covered

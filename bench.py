@@ -574,11 +574,11 @@ def run_piecewise(args, dist, rank, world, device, sampler):
                            flops_convention="primary: flash-equivalent (each pair needs one of the two "
                                             "score products); secondary: the reference benchmark's 3 "
                                             "forward matmuls, backward x 8/3"),
-               roofline=tensor_roofline("backward call (delta + one-pass kernel per branch + dq conversion)",
+               roofline=tensor_roofline("backward call (delta + one launch of the one-pass kernel over both branches + two dq conversions)",
                                         bwd, ms_b, flops="flash-equivalent: 2.5 x forward",
                                         forward=dict(tflops=round(fwd / (ms_f * 1e-3) / 1e12, 2),
                                                      frac_sustained=round(fwd / (ms_f * 1e-3) / 1e12 / load_peaks()["tflops_sustained"], 4))),
-               gpu_launches=6 * steps)
+               gpu_launches=5 * steps)   # forward, delta, the one-pass kernel, two dq conversions
     if args.skip_e2e:
         return rec
     host_in = [t.detach().cpu().pin_memory() for t in (q1, k1, q2, k2, v, do)]

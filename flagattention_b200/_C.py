@@ -18,7 +18,7 @@ FA_F16, FA_BF16 = 0, 1
 
 EXPORTED_SYMBOLS = (
     "fa_flash_fwd", "fa_splitkv_fwd", "fa_splitkv_combine", "fa_splitkv_workspace_bytes",
-    "fa_num_splits_heuristic", "fa_total_attention", "fa_flash_bwd_delta", "fa_flash_bwd_dkdv",
+    "fa_num_splits_heuristic", "fa_total_attention", "fa_flash_bwd_delta", "fa_flash_bwd_delta_zero", "fa_flash_bwd_dkdv",
     "fa_flash_bwd_dq", "fa_piecewise_fwd", "fa_piecewise_bwd_dkdv", "fa_piecewise_bwd_dq",
     "fa_paged_decode", "fa_paged_reduce", "fa_paged_workspace_bytes", "fa_paged_trace_blocks",
     "fa_paged_attention_noalloc", "fa_dropout_mask",

@@ -19,10 +19,20 @@ namespace fa {
 // in flight per thread); a block stays inside one (batch, head) pair, so the only divisions are
 // one per block and shifts.
 constexpr int kDeltaRows = 4;
+// `zero` (may be null): a buffer of `zero_granules` 16-byte granules that the same launch fills
+// with zeros, every block an equal contiguous share: the workspace of the one-pass backward,
+// whose zero-fill is a memory-bound pass over a different buffer and rides with this one.
 template <typename T, int D>
 __global__ void bwd_delta_kernel(const void *o, Strides so, const void *d_o, Strides sdo,
-                                 float *delta, int B, int H, int M, int blocks_per_pair) {
+                                 float *delta, int B, int H, int M, int blocks_per_pair,
+                                 uint4 *zero, long long zero_granules) {
   constexpr int LPR = D / 8;  // lanes per row
+  if (zero) {
+    const long long share = (zero_granules + gridDim.x - 1) / gridDim.x;
+    const long long begin = share * blockIdx.x;
+    const long long end = begin + share < zero_granules ? begin + share : zero_granules;
+    for (long long g = begin + threadIdx.x; g < end; g += blockDim.x) zero[g] = make_uint4(0u, 0u, 0u, 0u);
+  }
   const int bh = blockIdx.x / blocks_per_pair;
   const int rows_per_pass = blockDim.x / LPR;
   const int m0 = (blockIdx.x - bh * blocks_per_pair) * (rows_per_pass * kDeltaRows) +

@@ -10,6 +10,8 @@ struct DeltaLaunch {
   const fa_tensor4 *o, *d_o;
   float *delta;
   cudaStream_t stream;
+  void *zero = nullptr;        // optional buffer to fill with zeros in the same launch
+  int64_t zero_bytes = 0;
   template <typename T, int D>
   int operator()() const {
     const int threads = 256;
@@ -17,10 +19,11 @@ struct DeltaLaunch {
     const int64_t blocks_per_pair = (s->M + rows_per_block - 1) / rows_per_block;
     const int64_t blocks = blocks_per_pair * s->B * s->H;
     if (blocks > 0x7fffffff) return FA_ERR_TOO_LARGE;
-    if (blocks == 0) return FA_OK;
+    if (blocks == 0)
+      return (zero && cudaMemsetAsync(zero, 0, (size_t)zero_bytes, stream) != cudaSuccess) ? FA_ERR_LAUNCH : FA_OK;
     bwd_delta_kernel<T, D><<<(unsigned)blocks, threads, 0, stream>>>(
         o->ptr, strides_of(o), d_o->ptr, strides_of(d_o), delta, s->B, s->H, s->M,
-        (int)blocks_per_pair);
+        (int)blocks_per_pair, static_cast<uint4 *>(zero), (long long)(zero_bytes / 16));
     FA_CHECK_LAUNCH();
     return FA_OK;
   }
@@ -118,6 +121,18 @@ extern "C" int fa_flash_bwd_delta(const fa_flash_shape *s, const fa_tensor4 *o,
   if (!delta) return FA_ERR_BAD_ARG;
   return dispatch_dtype_d(s->dtype, s->D,
                           DeltaLaunch{s, o, d_o, delta, static_cast<cudaStream_t>(stream)});
+}
+
+extern "C" int fa_flash_bwd_delta_zero(const fa_flash_shape *s, const fa_tensor4 *o,
+                                       const fa_tensor4 *d_o, float *delta, void *zero,
+                                       int64_t zero_bytes, void *stream) {
+  if (int st = validate_shape(s)) return st;
+  if (int st = validate_tensors({o, d_o})) return st;
+  if (!delta || !zero || zero_bytes <= 0 || zero_bytes % 16 || (reinterpret_cast<uintptr_t>(zero) & 15))
+    return FA_ERR_BAD_ARG;
+  DeltaLaunch l{s, o, d_o, delta, static_cast<cudaStream_t>(stream)};
+  l.zero = zero, l.zero_bytes = zero_bytes;
+  return dispatch_dtype_d(s->dtype, s->D, l);
 }
 
 static BwdParams make_bwd(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 *k,

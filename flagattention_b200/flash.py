@@ -214,29 +214,35 @@ def _backward(q, k, v, o, L, do, causal, sm_scale, mark=None, dropout_p=0.0, see
         tdk, tdv, tdq = _C.tensor4(dk), _C.tensor4(dv), _C.tensor4(dq)
         if mark:
             mark("start")
-        st = lib.fa_flash_bwd_delta(_C.byref(shape), _C.byref(to), _C.byref(tdo),
-                                    _C.fptr(delta), stream)
-        _C.check(st, "fa_flash_bwd_delta")
-        if mark:
-            mark("delta")
         ws_bytes = (lib.fa_flash_bwd_fused_workspace_bytes(_C.byref(shape))
                     if use_one_pass_backward() else 0)
         if ws_bytes > 0:
-            # one pass over the score tiles; dq is accumulated in an fp32 workspace
+            # one pass over the score tiles; dq is accumulated in an fp32 workspace, which the
+            # delta kernel fills with zeros on its way (two memory-bound passes in one launch)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+            st = lib.fa_flash_bwd_delta_zero(_C.byref(shape), _C.byref(to), _C.byref(tdo), _C.fptr(delta),
+                                             _C.fptr(ws), ctypes.c_int64(ws_bytes), stream)
+            _C.check(st, "fa_flash_bwd_delta_zero")
+        else:
+            st = lib.fa_flash_bwd_delta(_C.byref(shape), _C.byref(to), _C.byref(tdo),
+                                        _C.fptr(delta), stream)
+            _C.check(st, "fa_flash_bwd_delta")
+        if mark:
+            mark("delta")
+        if ws_bytes > 0:
             args = (_C.byref(shape), _C.byref(tq), _C.byref(tk), _C.byref(tv), _C.byref(tdo),
                     _C.fptr(L), _C.fptr(delta), _C.byref(tdq), _C.byref(tdk), _C.byref(tdv),
                     _C.fptr(ws), ctypes.c_int64(ws_bytes))
             if mark:
-                # the three parts of the call one by one, so that each can be timed
+                # the parts of the call one by one, so that each can be timed
                 st = 0
-                for stage, name in ((1, "dq_zero"), (2, "dkdvdq"), (4, "dq_convert")):
+                for stage, name in ((2, "dkdvdq"), (4, "dq_convert")):
                     st = lib.fa_flash_bwd_fused_stages(*args, stage, stream)
                     if st != 0:
                         break
                     mark(name)
             else:
-                st = lib.fa_flash_bwd_fused(*args, stream)
+                st = lib.fa_flash_bwd_fused_stages(*args, 6, stream)   # kernel + dq conversion
             # a layout the one-pass kernel cannot map (a broadcast stride) goes to the pair below
             if st != _C.FA_ERR_UNSUPPORTED:
                 _C.check(st, "fa_flash_bwd_fused")

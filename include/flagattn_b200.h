@@ -113,6 +113,13 @@ int fa_total_attention(const fa_flash_shape *s, const fa_tensor4 *q, const fa_te
 int fa_flash_bwd_delta(const fa_flash_shape *s, const fa_tensor4 *o, const fa_tensor4 *d_o,
                        float *delta, void *stream);
 
+/* The same, and in the same launch `zero_bytes` bytes at `zero` are filled with zeros (16-byte
+ * aligned, a multiple of 16): the workspace of fa_flash_bwd_fused, whose zero-fill is a second
+ * memory-bound pass over another buffer; follow it with fa_flash_bwd_fused_stages(..., stages = 6).
+ * No counterpart in the reference. */
+int fa_flash_bwd_delta_zero(const fa_flash_shape *s, const fa_tensor4 *o, const fa_tensor4 *d_o,
+                            float *delta, void *zero, int64_t zero_bytes, void *stream);
+
 /* dk, dv with Hk heads: the sum over the query heads of a GQA group is taken
  * inside the kernel.  Replaces `_bwd_kv_kernel` and the host-side group sum
  * (src/flag_attn/flash.py:204-227,250-251; kernel :571-745). */

@@ -82,6 +82,11 @@ def test_one_pass_backward_and_cache_writer_validation_needs_no_gpu(built_lib):
     assert call(ctypes.c_void_p(0x1000), 1 << 30, 8) == -1
     assert lib.fa_flash_bwd_fused(ctypes.byref(small), *tensors, f, f, *outs, ctypes.c_void_p(0x1000),
                                   ctypes.c_int64(1 << 30), None) == -2
+    # delta + zero-fill in one launch: the buffer must be there, 16-byte aligned, a multiple of 16 bytes
+    dz = lambda ptr, nbytes: lib.fa_flash_bwd_delta_zero(ctypes.byref(shape), ctypes.byref(t), ctypes.byref(t), f,
+                                                        ptr, ctypes.c_int64(nbytes), None)
+    assert dz(None, 1024) == -1 and dz(ctypes.c_void_p(0x1000), 0) == -1
+    assert dz(ctypes.c_void_p(0x1000), 1000) == -1 and dz(ctypes.c_void_p(0x1008), 1024) == -1
     i64 = ctypes.c_int64
     app = lambda dtype, head, key: lib.fa_paged_cache_append(
         dtype, 4, 2, head, 16, key, f, i64(256), i64(128), f, f, i64(4096), i64(2048), i64(128), f, None)

@@ -107,3 +107,23 @@ def test_generic_kernels_at_tensor_core_head_dims(B, H, M, N, D, causal):
         assert_within_2x(o, o_ref, o_tor, f"o generic={mode}")
         for name, h, r, t in zip(("dq1", "dk1", "dq2", "dk2", "dv"), g, g_ref, g_tor):
             assert_within_2x(h, r, t, f"{name} generic={mode}")
+
+
+def test_dv_of_the_one_pass_backward_is_rounded_once():
+    """The one-pass backward walks every key block twice in one launch (near tiles, then far tiles)
+    and keeps dV in fp32 across both walks, so dV sees one rounding to 16 bits; the two-kernel mode
+    launches per branch and adds the far branch's dV to the near branch's 16-bit result.  Against
+    the fp32 oracle the one-pass dV must therefore be at least as close on average."""
+    from flagattention_b200 import flash as fl
+    B, H, L, D, w = 1, 4, 1024, 128, 300
+    q1, k1, q2, k2, v, do = _inputs(B, H, L, L, D, torch.bfloat16, "BHTD", 1.0, seed=77)
+    ins = [t.requires_grad_() for t in (q1, k1, q2, k2, v)]
+    o_ref = oracle.piecewise_attention(*ins, w, True, upcast=True)
+    dv_ref = torch.autograd.grad(o_ref, ins, do)[4].float()
+    err = {}
+    for mode in ("one_pass", "two_kernel"):
+        with fl.backward_mode(mode):
+            o = fa.piecewise_attention(*ins, w, causal=True)
+            dv = torch.autograd.grad(o, ins, do)[4].float()
+        err[mode] = (dv - dv_ref).abs().mean().item()
+    assert err["one_pass"] <= err["two_kernel"] * 1.02, err

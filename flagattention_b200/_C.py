@@ -99,11 +99,13 @@ FA_ERR_UNSUPPORTED = -2
 class kernel_family:
     """Context manager around fa_set_kernel_family: `with kernel_family("generic"):` runs the
     flash / piecewise operators on the shape-generic kernels only, "auto" on the tcgen05 kernels
-    wherever they cover the call.  Process-wide while active."""
+    wherever they cover the call, "one_cta_per_tile" on the tcgen05 kernels but with the forward's
+    one-CTA-per-query-tile form where "auto" would take the persistent one.  Process-wide while
+    active."""
 
     def __init__(self, family):
-        assert family in ("auto", "generic")
-        self.family = 1 if family == "generic" else 0
+        assert family in ("auto", "generic", "one_cta_per_tile")
+        self.family = {"auto": 0, "generic": 1, "one_cta_per_tile": 2}[family]
 
     def __enter__(self):
         self.previous = load().fa_set_kernel_family(self.family)

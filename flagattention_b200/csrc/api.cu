@@ -25,6 +25,10 @@ int *device_status_word() {
   return static_cast<int *>(ptr);
 }
 
+namespace tc {
+int reset_fwd_sched();   // flash_fwd_tc.cu
+}
+
 }  // namespace fa
 
 extern "C" const char *fa_status_string(int status) {
@@ -63,6 +67,8 @@ extern "C" int fa_device_status(int32_t *out, int32_t clear) {
     int zero = 0;
     if (cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess)
       return FA_ERR_LAUNCH;
+    // a forward launch that gave up may have left its work-item counter mid-way
+    if (fa::tc::reset_fwd_sched() != FA_OK) return FA_ERR_LAUNCH;
   }
   return FA_OK;
 }

@@ -369,7 +369,11 @@ int fa_debug_wait_probe(int64_t limit_cycles, int32_t *left_flag, void *stream);
 /* Kernel family used by the flash / piecewise entry points: 0 (default) = tcgen05 kernels where
  * they cover the call (head_dim 64 / 128, no dropout, layouts a tensor map can express), the
  * shape-generic mma.sync kernels elsewhere; 1 = shape-generic kernels only (what the tests use to
- * cross-check the two families).  Process-wide; returns the previous value.  The environment
+ * cross-check the two families); 2 = as 0, but fa_flash_fwd launches one CTA per query tile even
+ * where it would run its persistent kernel (calls with more query tiles than two per SM; that
+ * kernel keeps its work-item counter in a table of 64 words inside the library, one word per
+ * launch in turn, so more than 64 forward launches running at the same moment on one device
+ * would share a word).  Process-wide; returns the previous value.  The environment
  * variable FLAGATTN_B200_GENERIC=1 sets the initial value.  No counterpart in the reference. */
 int32_t fa_set_kernel_family(int32_t family);
 

@@ -1,5 +1,6 @@
 """GPU parity of flash_attention against the oracle, over the reference's own shape matrix
 (tests/flag_attn/test_flash_attention.py there) and the golden fixtures."""
+import ctypes
 import os
 
 import pytest
@@ -518,3 +519,27 @@ def test_ring_attention_of_one_rank_is_flash_attention(tmp_path):
         assert max_diff(g[0], g_ref[0]) <= 2 ** -7 * g_ref[0].float().abs().max().item()
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B,H,Hk,M,N,D,causal,dtype", [
+    (4, 32, 32, 4096, 4096, 128, True, torch.bfloat16),     # the benchmark shape
+    (64, 16, 16, 512, 512, 128, True, torch.bfloat16),      # many short query tiles
+    (8, 16, 4, 1000, 1300, 64, True, torch.float16),        # ragged, GQA, M < N
+    (8, 16, 16, 1300, 1000, 128, True, torch.float16),      # M > N: the first query rows see no key
+    (6, 12, 12, 777, 901, 128, False, torch.bfloat16),
+])
+def test_persistent_forward_equals_one_cta_per_tile(B, H, Hk, M, N, D, causal, dtype):
+    """With more query tiles than two per SM the forward runs as a persistent kernel (two CTAs per
+    SM working through the tiles); it computes every tile exactly as the one-CTA-per-tile kernel
+    does, so o and the log-normaliser must agree bit for bit, call after call (the work-item
+    counter goes back to zero by itself)."""
+    gen = torch.Generator().manual_seed(M * 7 + N)
+    q = torch.randn((B, H, M, D), generator=gen).to(dtype).cuda()
+    k, v = (torch.randn((B, Hk, N, D), generator=gen).to(dtype).cuda() for _ in range(2))
+    with _C.kernel_family("one_cta_per_tile"):
+        o_ref, lse_ref = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)[:2]
+    for _ in range(3):
+        o, lse = fa.flash_attention(q, k, v, causal, return_log_normalizer=True)[:2]
+        assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+    out = ctypes.c_int32(-1)
+    assert _C.load().fa_device_status(ctypes.byref(out), 0) == 0 and out.value == 0

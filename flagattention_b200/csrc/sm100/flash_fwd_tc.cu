@@ -57,10 +57,10 @@ static int launch_fwd_tc(const fa_flash_shape *s, int w, const fa_tensor4 *q, co
 
 // Work-item counters of the persistent forward.  The forward entry points take no workspace, so
 // the counters live in the library: a table of 64 words per device, one word per launch, taken
-// round-robin.  A launch leaves its word at zero (the last fetch of the launch resets it), and a
-// word is only touched while its kernel runs, so two launches collide only if 64 later launches
-// start while the first still runs.  fa_device_status(.., clear = 1) zeroes the table after a wait
-// that ran out (which leaves a counter mid-way).
+// round-robin, zeroed by a four-byte stream-ordered memset in front of the launch (a launch also
+// puts its word back to zero with its last fetch, but relying on that alone let one cut-short
+// launch spoil a later one: seen in the test suite).  A word is only touched while its kernel
+// runs, so two launches collide only if 64 later launches start while the first still runs.
 static __device__ unsigned g_fwd_sched[64];
 static unsigned *fwd_sched_table() {
   static std::atomic<unsigned *> base[64];
@@ -125,6 +125,7 @@ static int launch_fwd_persist(const fa_flash_shape *s, const fa_tensor4 *q, cons
   if (items <= 0 || items > (1ll << 30) || sms <= 0 || !fp.sched) return 1;
   fp.num_items = (int)items;
   dim3 grid((unsigned)(items < 2 * sms ? items : 2 * sms), 1, 1);
+  if (cudaMemsetAsync(fp.sched, 0, sizeof(unsigned), stream) != cudaSuccess) return FA_ERR_LAUNCH;
   kern<<<grid, C::kThreads, C::kTotal, stream>>>(mq, mk, mv, fp);
   FA_CHECK_LAUNCH();
   return FA_OK;

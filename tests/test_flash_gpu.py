@@ -531,8 +531,8 @@ def test_ring_attention_of_one_rank_is_flash_attention(tmp_path):
 def test_persistent_forward_equals_one_cta_per_tile(B, H, Hk, M, N, D, causal, dtype):
     """With more query tiles than two per SM the forward runs as a persistent kernel (two CTAs per
     SM working through the tiles); it computes every tile exactly as the one-CTA-per-tile kernel
-    does, so o and the log-normaliser must agree bit for bit, call after call (the work-item
-    counter goes back to zero by itself)."""
+    does, so o and the log-normaliser must agree bit for bit, call after call and whatever earlier
+    launches left in the library's table of work-item counters."""
     gen = torch.Generator().manual_seed(M * 7 + N)
     q = torch.randn((B, H, M, D), generator=gen).to(dtype).cuda()
     k, v = (torch.randn((B, Hk, N, D), generator=gen).to(dtype).cuda() for _ in range(2))

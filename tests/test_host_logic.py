@@ -247,3 +247,7 @@ def test_kernel_family_switch(built_lib):
     with _C.kernel_family("generic"):
         assert lib.fa_set_kernel_family(1) == 1
     assert lib.fa_set_kernel_family(0) == 0
+    with _C.kernel_family("one_cta_per_tile"):      # tcgen05 kernels, forward without its persistent form
+        assert lib.fa_set_kernel_family(2) == 2
+    assert lib.fa_set_kernel_family(7) == 0          # unknown values mean 0
+    assert lib.fa_set_kernel_family(0) == 0

@@ -142,9 +142,9 @@ int flash_fwd_tc(const fa_flash_shape *s, const fa_tensor4 *q, const fa_tensor4 
   if (!covered(s)) return 1;
   // More query tiles than CTA slots and short walks (or head_dim 64): the persistent kernel.  It
   // measured +3..5 % at N <= 1024 and at head_dim 64, but -10 % at head_dim 128 and N = 4096, -17 %
-  // at 16384: its two CTAs per SM start together and walk items of equal length in step, so they
-  // want the tensor pipe and the exponential unit at the same moments (steady tile period 1750-1840
-  // clocks against 1534 for CTAs that come and go one by one).
+  // at 16384: its steady tile period is 1750-1840 clocks against 1534 of the one-CTA-per-tile
+  // kernel (why is not known: starting the second CTA of every SM a fraction of a tile period late,
+  // in case the two walked in step, changed nothing).
   const bool short_walks = s->D == 64 || s->N <= 1536;
   if (!one_cta_per_tile_forced() && short_walks &&
       (int64_t)((s->M + 127) / 128) * s->B * s->H > 2 * (int64_t)sm_count_fwd()) {

@@ -203,22 +203,27 @@ def barrier(dist):
     torch.cuda.synchronize()
 
 
+def extra_warmup_calls(dist, device, warm, warm_seconds, spent):
+    """How many more warm-up calls to make after `warm` calls took `spent` seconds, so that the
+    warm-up lasts about `warm_seconds`: each rank proposes a count from its own pace and the largest
+    wins, so every rank makes the same number (the timed function may hold a collective)."""
+    extra = 0
+    if spent < warm_seconds:
+        extra = int((warm_seconds - spent) / max(spent / max(warm, 1), 1e-5)) + 1
+    return int(max_over_ranks(dist, float(extra), device))
+
+
 def timed(fn, steps, dist, device, warm=3, warm_seconds=0.0):
     """`warm` untimed calls (continued until `warm_seconds` of load), then, after a barrier among the
     ranks and with no idle gap on this GPU, `steps` timed calls; returns (ms per call, max over
     ranks; per-call device times of this rank)."""
-    # The number of warm-up calls must be the same on every rank (fn may hold a collective): each
-    # rank proposes a count from its own pace, the largest wins.
     t_w = time.perf_counter()
     for _ in range(warm):
         fn()
     extra = 0
     if warm_seconds > 0.0:
         torch.cuda.synchronize()
-        spent = time.perf_counter() - t_w
-        if spent < warm_seconds:
-            extra = int((warm_seconds - spent) / max(spent / max(warm, 1), 1e-5)) + 1
-        extra = int(max_over_ranks(dist, float(extra), device))
+        extra = extra_warmup_calls(dist, device, warm, warm_seconds, time.perf_counter() - t_w)
     for i in range(extra):
         fn()
         if i % 8 == 7:

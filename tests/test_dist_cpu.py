@@ -79,6 +79,34 @@ def test_two_rank_gloo_shard_and_gather(tmp_path):
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
 
 
+def _warmup_worker(rank, world, port, result_dir):
+    import importlib.util
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+        bench = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(bench)
+        # the ranks ran their first calls at different paces: rank 0 fast, rank 1 slow, rank 2 done already
+        spent = [0.01, 0.2, 0.9][rank]
+        n = bench.extra_warmup_calls(dist, torch.device("cpu"), 5, 0.5, spent)
+        assert n == int((0.5 - 0.01) / (0.01 / 5)) + 1          # the fastest rank's proposal, on every rank
+        assert bench.extra_warmup_calls(dist, torch.device("cpu"), 5, 0.5, 0.7) == 0
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_warmup_count_of_the_benchmark_is_the_same_on_every_rank(tmp_path):
+    """bench.py warms up "for half a second"; the number of calls that takes must be agreed among the
+    ranks, because a timed function may contain a collective (ranks that disagreed hung the 4- and
+    8-GPU runs once)."""
+    world = 3
+    mp.spawn(_warmup_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
 def _ring_worker(rank, world, port, result_dir):
     import torch.distributed as dist
     from flagattention_b200 import testing

@@ -995,8 +995,9 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="no cfg3 / sweep / decode / rotary / strong records")
     ap.add_argument("--backward", default="auto", choices=["auto", "one_pass", "two_kernel"],
                     help="backward kernels of the dense operators (flagattention_b200.flash.set_backward_mode)")
-    ap.add_argument("--kernels", default="auto", choices=["auto", "generic"],
-                    help="generic: the shape-generic mma.sync kernels instead of the tcgen05 ones (profiling)")
+    ap.add_argument("--kernels", default="auto", choices=["auto", "generic", "one_cta_per_tile"],
+                    help="generic: the shape-generic mma.sync kernels instead of the tcgen05 ones; "
+                         "one_cta_per_tile: tcgen05, but the forward never in its persistent form (profiling)")
     ap.add_argument("--only", default=None, choices=["flash", "paged", "piecewise", "rotary", "cfg3", "sweep", "total"],
                     help="run one workload only (profiling); the JSON line is then partial")
     ap.add_argument("--paged-seqs", type=int, default=PAGED_CFG["num_seqs"],
@@ -1018,7 +1019,7 @@ def main():
     from flagattention_b200 import _C as fa_c
     from flagattention_b200 import flash as fa_flash
     fa_flash.set_backward_mode(args.backward)
-    fa_c.load().fa_set_kernel_family(1 if args.kernels == "generic" else 0)
+    fa_c.load().fa_set_kernel_family({"auto": 0, "generic": 1, "one_cta_per_tile": 2}[args.kernels])
 
     PAGED_CFG["num_seqs"] = args.paged_seqs
     single = {"paged": lambda: run_paged(args, dist, rank, world, device),
